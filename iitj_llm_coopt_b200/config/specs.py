@@ -99,6 +99,19 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class TokenInputSpec:
+    """What a layer reads of the token itself, beside the stream: `dim` columns, from `offset` on, of a second
+    embedding table whose rows are `table_width` wide (the embedding part owns the table)."""
+    kind: str                    # key in parts.TOKEN_INPUTS
+    width: int
+    dim: int
+    offset: int
+    table_width: int
+    eps: float = 1e-6
+    options: tuple = ()
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: `arrangement` names how the parts are wired (parts.ARRANGEMENTS); `parts` holds one spec record
     for each part name the arrangement declares (its PARTS), as (name, spec) pairs.  `LayerSpec.of("prenorm",

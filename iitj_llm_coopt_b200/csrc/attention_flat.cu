@@ -8,10 +8,13 @@
 //                      every head's rotated query part written behind the place of its absorbed part in q_out.
 // llm_headnorm_store:  per token, every query head and key head divided by its root mean square and multiplied by a
 //                      gain vector shared by all heads (optional); queries in place, keys and values into the cache.
-// llm_attention_flat:  softmax(scale * q . k) over the keys [max(0, p - window + 1), p] (window 0: from 0), times the
-//                      values, optionally times sigmoid(gate[token, head]).  One warp per (token, head); keys are walked in
-//                      tiles of 32 that start at multiples of 32 of the key position, so a row's sums run in an order that
-//                      depends on its own position alone.
+// llm_attention_flat:  softmax(score) over the keys [max(0, p - window + 1), p] (window 0: from 0), times the values,
+//                      optionally times sigmoid(gate) (one gate number per head, or one per output number).  The score of
+//                      query position p and key position j is  s = scale * temp(p) * q . k,  then  s = cap * tanh(s / cap)
+//                      (cap > 0),  then  s -= slope[head] * (p - j)  (slopes given), with the query temperature
+//                      temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)  (every > 0).  One warp per (token, head); keys are
+//                      walked in tiles of 32 that start at multiples of 32 of the key position, so a row's sums run in an
+//                      order that depends on its own position alone.
 #include "common.cuh"
 
 namespace {
@@ -34,7 +37,8 @@ __device__ __forceinline__ void rotate_row(const TI* __restrict__ in, TO* __rest
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ qd, int ld, const float* __restrict__ cos, const float* __restrict__ sin, int rotary_dim,
+latent_prepare_kernel(const T* __restrict__ qd, int ld, const T* __restrict__ kv, int ld_kv, const float* __restrict__ cos,
+                      const float* __restrict__ sin, int rotary_dim,
                       int interleaved, const float* __restrict__ gain, float eps, T* __restrict__ q_out, T* __restrict__ cache,
                       const int* __restrict__ slots, long long page_stride, int page_size, int heads, int dim, int rot_dim, int rank) {
     pdl_trigger();
@@ -42,7 +46,8 @@ latent_prepare_kernel(const T* __restrict__ qd, int ld, const float* __restrict_
     __shared__ float red[32];
     const int t = blockIdx.x;
     const T* row = qd + (size_t)t * ld;
-    const int qw = heads * (dim + rot_dim), out_row = rank + rot_dim;
+    const T* low = kv + (size_t)t * ld_kv;             // [rank latent numbers | rot_dim numbers of the shared key part]
+    const int out_row = rank + rot_dim;
     const float* cos_t = cos ? cos + (size_t)t * (rotary_dim / 2) : nullptr;
     const float* sin_t = sin ? sin + (size_t)t * (rotary_dim / 2) : nullptr;
     // every head's rotated query part
@@ -52,15 +57,15 @@ latent_prepare_kernel(const T* __restrict__ qd, int ld, const float* __restrict_
     // the latent row's statistics (all threads take part, whether the row is stored or not)
     float ss = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
-        const float v = to_f32(row[qw + i]);
+        const float v = to_f32(low[i]);
         ss += v * v;
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)rank + eps);
     if (!slots) return;
     const int slot = slots[t];
     T* dst = cache + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * out_row;
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(row[qw + i]) * inv * gain[i]);
-    rotate_row(row + qw + rank, dst + rank, rot_dim, rotary_dim, interleaved, cos_t, sin_t, threadIdx.x, blockDim.x);
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(low[i]) * inv * gain[i]);
+    rotate_row(low + rank, dst + rank, rot_dim, rotary_dim, interleaved, cos_t, sin_t, threadIdx.x, blockDim.x);
 }
 
 template <typename T>
@@ -137,9 +142,10 @@ template <typename T, int OWN>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_flat_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache, long long page_stride,
                       const int* __restrict__ block_table, int table_width, const int* __restrict__ token_request,
-                      const int* __restrict__ positions, const float* __restrict__ gate, T* __restrict__ out, int out_stride,
-                      int tokens, int heads, int kv_heads, int key_dim, int value_dim, int shared_value, int page_size,
-                      int window, float scale, int vec) {
+                      const int* __restrict__ positions, const float* __restrict__ gate, int gate_cols, T* __restrict__ out,
+                      int out_stride, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int shared_value,
+                      int page_size, int window, float scale, float softcap, const float* __restrict__ slopes, float temp_coef,
+                      int temp_every, int vec) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float q_smem[];
@@ -151,6 +157,9 @@ attention_flat_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* table = block_table + (size_t)token_request[t] * table_width;
+    if (temp_every > 0) scale *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+    const float slope = slopes ? slopes[h] : 0.f;
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
 
     float* qs = q_smem + (size_t)warp * ((key_dim + 3) & ~3);
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * key_dim;
@@ -176,6 +185,8 @@ attention_flat_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
             koff = (long long)(page + key_head + (size_t)o * key_dim);
             voff = shared_value ? koff : (long long)(page + value_plane + (size_t)o * value_dim);
             s = scale * dot_any<T>(cache + koff, qs, key_dim, vec != 0);
+            if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+            s -= slope * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(s));   // finite: every tile holds a visible key
         const float corr = expf(m - m_new);          // 0 on the first tile (m = -inf)
@@ -198,17 +209,21 @@ attention_flat_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     }
     T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
     float inv = 1.0f / l;
-    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * heads + h]));
+    if (gate && gate_cols == 1) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * heads + h]));
+    const float* grow = gate && gate_cols > 1 ? gate + ((size_t)t * heads + h) * value_dim : nullptr;
 #pragma unroll
     for (int i = 0; i < OWN; ++i) {
         const int d = lane + 32 * i;
-        if (d < value_dim) orow[d] = from_f32<T>(acc[i] * inv);
+        if (d < value_dim) orow[d] = from_f32<T>(grow ? acc[i] * inv / (1.0f + expf(-grow[d])) : acc[i] * inv);
     }
 }
 
 }  // namespace
 
-LLM_API int llm_latent_prepare(const void* qd, int ld, const float* cos, const float* sin, int rotary_dim, int interleaved,
+// qd: rows of heads x (dim + rot_dim) query numbers (stride ld); kv: rows of rank + rot_dim numbers (stride ld_kv), which may
+// be columns of the same product as qd or of another one.
+LLM_API int llm_latent_prepare(const void* qd, int ld, const void* kv, int ld_kv, const float* cos, const float* sin,
+                               int rotary_dim, int interleaved,
                                const float* gain, float eps, void* q_out, void* cache, const int* slots, long long page_stride,
                                int page_size, int dtype, int tokens, int heads, int dim, int rot_dim, int rank, cudaStream_t stream) {
     if (tokens == 0) return 0;
@@ -216,8 +231,8 @@ LLM_API int llm_latent_prepare(const void* qd, int ld, const float* cos, const f
         LLM_FAIL(-1, "latent_prepare: rotary_dim %d must be even, at most rot_dim %d, and come with tables", rotary_dim, rot_dim);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        llm_launch(latent_prepare_kernel<T>, (unsigned)tokens, 128, 0, stream, (const T*)qd, ld, cos, sin, rotary_dim, interleaved,
-                   gain, eps, (T*)q_out, (T*)cache, slots, page_stride, page_size, heads, dim, rot_dim, rank);
+        llm_launch(latent_prepare_kernel<T>, (unsigned)tokens, 128, 0, stream, (const T*)qd, ld, (const T*)kv, ld_kv, cos, sin,
+                   rotary_dim, interleaved, gain, eps, (T*)q_out, (T*)cache, slots, page_stride, page_size, heads, dim, rot_dim, rank);
         LLM_CHECK_LAUNCH("latent_prepare");
         return 0;
     });
@@ -237,14 +252,17 @@ LLM_API int llm_headnorm_store(void* qkv, int ld, const float* q_gain, const flo
 }
 
 LLM_API int llm_attention_flat(const void* q, int q_stride, const void* cache, long long page_stride, const int* block_table,
-                               int table_width, const int* token_request, const int* positions, const float* gate, void* out,
-                               int out_stride, int dtype, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
-                               int shared_value, int page_size, int window, float scale, cudaStream_t stream) {
+                               int table_width, const int* token_request, const int* positions, const float* gate, int gate_cols,
+                               void* out, int out_stride, int dtype, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
+                               int shared_value, int page_size, int window, float scale, float softcap, const float* slopes,
+                               float temp_coef, int temp_every, cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (kv_heads <= 0 || heads % kv_heads) LLM_FAIL(-1, "attention_flat: heads %d is not a multiple of kv_heads %d", heads, kv_heads);
     if (value_dim <= 0 || value_dim > 512 || key_dim <= 0 || key_dim > 2048)
         LLM_FAIL(-1, "attention_flat: value_dim %d must be in [1, 512], key_dim %d in [1, 2048]", value_dim, key_dim);
     if (shared_value && value_dim > key_dim) LLM_FAIL(-1, "attention_flat: shared values are a part of the key rows");
+    if (gate && gate_cols != 1 && gate_cols != value_dim)
+        LLM_FAIL(-1, "attention_flat: a gate has one number per head or one per output number (%d, value_dim %d)", gate_cols, value_dim);
     const long long items = (long long)tokens * heads;
     const long long blocks = (items + kWarps - 1) / kWarps;
     if (blocks > 0x7fffffffLL) LLM_FAIL(-1, "attention_flat: too many (token, head) pairs: %lld", items);
@@ -255,8 +273,9 @@ LLM_API int llm_attention_flat(const void* q, int q_stride, const void* cache, l
         const int vec = !(key_dim % per) && !(page_stride % per) && !((uintptr_t)cache & 15);
 #define LLM_FLAT_CASE(OWN)                                                                                                  \
         llm_launch(attention_flat_kernel<T, OWN>, (unsigned)blocks, kWarps * 32, smem, stream, (const T*)q, q_stride,       \
-                   (const T*)cache, page_stride, block_table, table_width, token_request, positions, gate, (T*)out, out_stride, \
-                   tokens, heads, kv_heads, key_dim, value_dim, shared_value, page_size, window, scale, vec)
+                   (const T*)cache, page_stride, block_table, table_width, token_request, positions, gate, gate_cols, (T*)out,     \
+                   out_stride, tokens, heads, kv_heads, key_dim, value_dim, shared_value, page_size, window, scale, softcap,    \
+                   slopes, temp_coef, temp_every, vec)
         if (value_dim <= 64) LLM_FLAT_CASE(2);
         else if (value_dim <= 128) LLM_FLAT_CASE(4);
         else if (value_dim <= 256) LLM_FLAT_CASE(8);

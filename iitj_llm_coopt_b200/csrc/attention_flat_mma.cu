@@ -31,7 +31,9 @@ struct FlatMmaArgs {
     const __nv_bfloat16* cache; long long page_stride;
     const int* block_table; int table_width;
     const int* tiles; int n_tiles;            // (first token row, tokens, position of the first, request)
-    const float* gate;
+    const float* gate; int gate_cols;         // one gate number per head (1) or per output number (value_dim)
+    const float* slopes;                      // per head: slope * (query position - key position) is taken off the score
+    float softcap, temp_coef; int temp_every; // score squashing and query temperature (0: none), as in attention_flat.cu
     __nv_bfloat16* out; int out_stride;
     float* part_o; float* part_ml;            // [token, head, split, value_dim] and [token, head, split, 2] when splits > 1
     int heads, kv_heads, key_dim, value_dim, shared_value, page_size, window, heads_per_block, tokens_per_tile, splits;
@@ -90,6 +92,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
     }
     // this thread's two rows (gq and gq + 8 of the warp's 16)
     int row_pos[2], row_lo[2];
+    float row_scale[2], row_slope[2];
     bool row_ok[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -98,7 +101,10 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         row_ok[e] = ti < ntok && hg < group;
         row_pos[e] = pos0 + ti;
         row_lo[e] = a.window > 0 ? max(0, row_pos[e] - a.window + 1) : 0;
+        row_scale[e] = a.temp_every > 0 ? a.scale * (1.0f + a.temp_coef * logf((float)((row_pos[e] + 1) / a.temp_every) + 1.0f)) : a.scale;
+        row_slope[e] = a.slopes && row_ok[e] ? a.slopes[kvh * group + hg] : 0.f;
     }
+    const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
     const bool warp_live = (warp * 16) / hpb < ntok;
     float o[NT][4];
 #pragma unroll
@@ -188,7 +194,9 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
                 for (int c = 0; c < 2; ++c) {
                     const int key = k0 + j * 8 + 2 * tq + c;
                     const bool seen = row_ok[e] && key <= row_pos[e] && key >= row_lo[e];
-                    const float v = seen ? s[j][2 * e + c] * a.scale : -INFINITY;
+                    float v = s[j][2 * e + c] * row_scale[e];
+                    if (a.softcap > 0.f) v = a.softcap * tanhf(v * inv_cap);
+                    v = seen ? v - row_slope[e] * (float)(row_pos[e] - key) : -INFINITY;
                     s[j][2 * e + c] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -250,12 +258,20 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         const int t = row0 + r / hpb, head = kvh * group + hb * hpb + r % hpb;
         if (a.splits == 1) {
             float inv = 1.0f / l[e];
-            if (a.gate) inv *= 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.heads + head]));
+            if (a.gate && a.gate_cols == 1) inv *= 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.heads + head]));
+            const float* grow = a.gate && a.gate_cols > 1 ? a.gate + ((size_t)t * a.heads + head) * a.value_dim + slice0 : nullptr;
             bf16* dst = a.out + (size_t)t * a.out_stride + (size_t)head * a.value_dim + slice0;
 #pragma unroll
             for (int n = 0; n < NT; ++n)
-                if (slice0 + n * 8 < a.value_dim)
-                    *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * tq) = pack_bf16(o[n][2 * e] * inv, o[n][2 * e + 1] * inv);
+                if (slice0 + n * 8 < a.value_dim) {
+                    float g0 = inv, g1 = inv;
+                    if (grow) {
+                        const float2 g = *reinterpret_cast<const float2*>(grow + n * 8 + 2 * tq);
+                        g0 = inv / (1.0f + expf(-g.x));
+                        g1 = inv / (1.0f + expf(-g.y));
+                    }
+                    *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * tq) = pack_bf16(o[n][2 * e] * g0, o[n][2 * e + 1] * g1);
+                }
         } else {
             const size_t item = ((size_t)t * a.heads + head) * a.splits + split;
             float* dst = a.part_o + item * a.value_dim + slice0;
@@ -273,7 +289,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
 
 // out[t, head] = sum_s O_s e^(m_s - m) / sum_s l_s e^(m_s - m), times the gate; one block per (token, head).
 __global__ void __launch_bounds__(128)
-flat_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ gate,
+flat_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ gate, int gate_cols,
                   __nv_bfloat16* __restrict__ out, int out_stride, int heads, int value_dim, int splits) {
     pdl_trigger();
     pdl_wait();
@@ -284,13 +300,14 @@ flat_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     float l = 0.f;
     for (int s = 0; s < splits; ++s) l += ml[2 * s + 1] * (ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m));
     float inv = 1.0f / l;
-    if (gate) inv *= 1.0f / (1.0f + expf(-gate[item]));
+    if (gate && gate_cols == 1) inv *= 1.0f / (1.0f + expf(-gate[item]));
+    const float* grow = gate && gate_cols > 1 ? gate + item * value_dim : nullptr;
     const size_t t = item / heads, h = item % heads;
     for (int d = threadIdx.x; d < value_dim; d += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < splits; ++s)
             if (ml[2 * s] != -INFINITY) acc += part_o[(item * splits + s) * value_dim + d] * expf(ml[2 * s] - m);
-        out[t * out_stride + h * value_dim + d] = __float2bfloat16_rn(acc * inv);
+        out[t * out_stride + h * value_dim + d] = __float2bfloat16_rn(grow ? acc * inv / (1.0f + expf(-grow[d])) : acc * inv);
     }
 }
 
@@ -322,18 +339,22 @@ LLM_API int llm_attention_flat_mma_heads_per_block(int heads, int kv_heads) {
 // tiles [n_tiles, 4]: (first token row, tokens <= 64 / heads_per_block, position of the first, request).  splits > 1 needs
 // part_o [tokens, heads, splits, value_dim] and part_ml [tokens, heads, splits, 2] float32 and runs the merge after.
 LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cache, long long page_stride, const int* block_table,
-                                   int table_width, const int* tiles, int n_tiles, const float* gate, void* out, int out_stride,
-                                   int tokens, int heads, int kv_heads, int key_dim, int value_dim, int shared_value, int page_size,
-                                   int window, float scale, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                   int table_width, const int* tiles, int n_tiles, const float* gate, int gate_cols, void* out,
+                                   int out_stride, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int shared_value,
+                                   int page_size, int window, float scale, float softcap, const float* slopes, float temp_coef,
+                                   int temp_every, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
     if (n_tiles == 0) return 0;
     if (!llm_attention_flat_mma_supported(heads, kv_heads, key_dim, value_dim, shared_value, page_stride))
         LLM_FAIL(-1, "attention_flat_mma: sizes not taken (key_dim %d, value_dim %d)", key_dim, value_dim);
+    if (gate && gate_cols != 1 && gate_cols != value_dim)
+        LLM_FAIL(-1, "attention_flat_mma: a gate has one number per head or one per output number (%d, value_dim %d)", gate_cols, value_dim);
     if (splits < 1) splits = 1;
     if (splits > 1 && (!part_o || !part_ml)) LLM_FAIL(-1, "attention_flat_mma: key splits need partial buffers");
     if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || q_stride % 8) LLM_FAIL(-1, "attention_flat_mma: rows must start on 16 bytes");
     FlatMmaArgs a;
     a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride; a.cache = (const __nv_bfloat16*)cache; a.page_stride = page_stride;
     a.block_table = block_table; a.table_width = table_width; a.tiles = tiles; a.n_tiles = n_tiles; a.gate = gate;
+    a.gate_cols = gate_cols; a.slopes = slopes; a.softcap = softcap; a.temp_coef = temp_coef; a.temp_every = temp_every;
     a.out = (__nv_bfloat16*)out; a.out_stride = out_stride; a.part_o = part_o; a.part_ml = part_ml;
     a.heads = heads; a.kv_heads = kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.shared_value = shared_value;
     a.page_size = page_size; a.window = window; a.splits = splits; a.scale = scale;
@@ -359,7 +380,7 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
     LLM_CHECK_LAUNCH("attention_flat_mma");
     if (splits > 1) {
         llm_launch(flat_merge_kernel, (unsigned)(tokens * heads), 128, 0, stream, (const float*)part_o, (const float*)part_ml, gate,
-                   (__nv_bfloat16*)out, out_stride, heads, value_dim, splits);
+                   gate_cols, (__nv_bfloat16*)out, out_stride, heads, value_dim, splits);
         LLM_CHECK_LAUNCH("attention_flat_merge");
     }
     return 0;

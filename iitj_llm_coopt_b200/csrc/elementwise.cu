@@ -439,20 +439,25 @@ __global__ void rope_store_sum_kernel(const float* __restrict__ parts, int split
 // cos[t, i] = cos(positions[t] * inv_freq[i]), sin likewise: computed once per step and shared by all
 // layers with the same position encoding (float32 angles, float32 sincosf).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float* __restrict__ cos_table, float* __restrict__ sin_table, int tokens, int half) {
+                                  float* __restrict__ cos_table, float* __restrict__ sin_table, int tokens, int half,
+                                  float amplitude) {
     pdl_trigger();
     pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= tokens * half) return;
     const int t = idx / half, i = idx % half;
-    sincosf((float)positions[t] * inv_freq[i], &sin_table[idx], &cos_table[idx]);
+    float s, c;
+    sincosf((float)positions[t] * inv_freq[i], &s, &c);
+    sin_table[idx] = s * amplitude;       // a scaling law may make both grow by one factor (1: none)
+    cos_table[idx] = c * amplitude;
 }
 
 LLM_API int llm_rope_table(const int* positions, const float* inv_freq, float* cos_table, float* sin_table,
-                           int tokens, int half, cudaStream_t stream) {
+                           int tokens, int half, float amplitude, cudaStream_t stream) {
     if (tokens == 0 || half == 0) return 0;
     const int total = tokens * half;
-    llm_launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_table, sin_table, tokens, half);
+    llm_launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_table, sin_table, tokens, half,
+               amplitude);
     LLM_CHECK_LAUNCH("rope_table");
     return 0;
 }

@@ -7,8 +7,11 @@
 //   listed    a device list of tiles (group, first row, rows) over rows that were sorted by group beforehand (the experts
 //             of a routed feed-forward: llm_moe_plan writes the list and its count, so nothing comes back to the host);
 //             a row may be read through an index (`row_src`: sorted row -> token), the result row is the sorted row.
-// Epilogue "glu": W_g holds n gate rows and then n up rows, and the result is g * sigmoid(slope * g) * (u + 1) with
-// g = min(gate, limit), u = clamp(up, -limit, limit): the [rows, 2n] intermediate never exists.
+// Epilogue "glu": W_g holds n gate rows and then n up rows, and the [rows, 2n] intermediate never exists.  Form 1: the result is
+// g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).  Form 2: silu(w g) * (w u) with a
+// weight w per sorted row (null: 1), which is the product of the row scaled by w since the product is linear in the row.
+// Epilogue "out_gate" (without glu): every result number times the sigmoid of the float32 number at its place in a matrix laid out
+// like the result.
 //
 // bfloat16: mma.sync m16n8k16 with float32 accumulators, tiles of 64 rows x 64 columns x 32 k, four warps; float32: FMA
 // on the CUDA cores, no tensor cores, no TF32.  Every output element is summed over k in one fixed order, so a row's result
@@ -27,6 +30,8 @@ struct GroupedArgs {
     int M, N, K, groups, m_tiles;
     const int* tiles;          // listed mode: tiles[0] = count, entry i at tiles[4 + 4 * i] = (group, first row, rows, -)
     int glu; float limit, slope;
+    const float* row_scale;    // form 2 of the glu epilogue: a factor per result row
+    const float* out_gate;     // float32 laid out like C (same ldc and offsets): the result is multiplied by its sigmoid
     int vec_a, vec_w;
 };
 
@@ -55,6 +60,10 @@ __device__ __forceinline__ const T* a_row(const GroupedArgs& a, const Tile& t, i
 }
 
 __device__ __forceinline__ float glu(float g, float u, float limit, float slope) {
+    if (limit < 0.f) {                  // form 2: `slope` carries the row's weight
+        g *= slope;
+        return g / (1.0f + expf(-g)) * (u * slope);
+    }
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
@@ -164,6 +173,7 @@ grouped_bf16_kernel(const GroupedArgs a) {
         __syncthreads();
     }
     bf16* C = static_cast<bf16*>(a.C) + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride);
+    const float* G = a.out_gate ? a.out_gate + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride) : nullptr;
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -173,7 +183,9 @@ grouped_bf16_kernel(const GroupedArgs a) {
                 const int r = wm + i * 16 + gq + (e >> 1) * 8, n = n0 + wn + j * 8 + 2 * tq + (e & 1);
                 if (r < tile.rows && n < a.N) {
                     float v = acc[0][i][j][e];
-                    if (GLU) v = glu(v, acc[GLU ? 1 : 0][i][j][e], a.limit, a.slope);
+                    if (GLU) v = glu(v, acc[GLU ? 1 : 0][i][j][e], a.glu == 2 ? -1.f : a.limit,
+                                     a.glu == 2 ? (a.row_scale ? a.row_scale[tile.row0 + r] : 1.f) : a.slope);
+                    if (!GLU && G) v /= 1.0f + expf(-G[(long long)(tile.row0 + r) * a.ldc + n]);
                     C[(long long)(tile.row0 + r) * a.ldc + n] = __float2bfloat16_rn(v);
                 }
             }
@@ -271,6 +283,7 @@ grouped_bf16_pipe_kernel(const GroupedArgs a) {
         }
     }
     bf16* C = static_cast<bf16*>(a.C) + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride);
+    const float* G = a.out_gate ? a.out_gate + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride) : nullptr;
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -280,7 +293,9 @@ grouped_bf16_pipe_kernel(const GroupedArgs a) {
                 const int r = wm + i * 16 + gq + (e >> 1) * 8, n = n0 + wn + j * 8 + 2 * tq + (e & 1);
                 if (r < tile.rows && n < a.N) {
                     float v = acc[0][i][j][e];
-                    if (GLU) v = glu(v, acc[NW - 1][i][j][e], a.limit, a.slope);
+                    if (GLU) v = glu(v, acc[NW - 1][i][j][e], a.glu == 2 ? -1.f : a.limit,
+                                     a.glu == 2 ? (a.row_scale ? a.row_scale[tile.row0 + r] : 1.f) : a.slope);
+                    if (!GLU && G) v /= 1.0f + expf(-G[(long long)(tile.row0 + r) * a.ldc + n]);
                     C[(long long)(tile.row0 + r) * a.ldc + n] = __float2bfloat16_rn(v);
                 }
             }
@@ -354,6 +369,7 @@ grouped_f32_kernel(const GroupedArgs a) {
         __syncthreads();
     }
     float* C = static_cast<float*>(a.C) + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride);
+    const float* G = a.out_gate ? a.out_gate + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride) : nullptr;
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int r = tr * TM + i;
@@ -363,7 +379,9 @@ grouped_f32_kernel(const GroupedArgs a) {
             const int n = n0 + tc * TN + j;
             if (n >= a.N) continue;
             float v = acc[0][i][j];
-            if (GLU) v = glu(v, acc[GLU ? 1 : 0][i][j], a.limit, a.slope);
+            if (GLU) v = glu(v, acc[GLU ? 1 : 0][i][j], a.glu == 2 ? -1.f : a.limit,
+                             a.glu == 2 ? (a.row_scale ? a.row_scale[tile.row0 + r] : 1.f) : a.slope);
+            if (!GLU && G) v /= 1.0f + expf(-G[(long long)(tile.row0 + r) * a.ldc + n]);
             C[(long long)(tile.row0 + r) * a.ldc + n] = v;
         }
     }
@@ -380,7 +398,7 @@ LLM_API int llm_gemm_grouped_tile_rows() { return BM; }
 LLM_API int llm_gemm_grouped(const void* A, long long lda, long long a_group_stride, long long a_offset, const int* row_src,
                              const void* W, void* C, long long ldc, long long c_group_stride, long long c_offset, int dtype,
                              int M, int N, int K, int groups, const int* tiles, int max_tiles, int glu, float limit, float slope,
-                             cudaStream_t stream) {
+                             const float* row_scale, const float* out_gate, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || groups <= 0) return 0;
     if (!tiles && M <= 0) return 0;
     if (tiles && max_tiles <= 0) return 0;
@@ -389,7 +407,10 @@ LLM_API int llm_gemm_grouped(const void* A, long long lda, long long a_group_str
     a.W = W; a.w_group_stride = (long long)(glu ? 2 : 1) * N * K;
     a.C = C; a.ldc = ldc; a.c_group_stride = c_group_stride; a.c_offset = c_offset;
     a.M = M; a.N = N; a.K = K; a.groups = groups; a.m_tiles = tiles ? 0 : (M + BM - 1) / BM;
-    a.tiles = tiles; a.glu = glu; a.limit = limit; a.slope = slope;
+    a.tiles = tiles; a.glu = glu; a.limit = limit; a.slope = slope; a.row_scale = row_scale; a.out_gate = out_gate;
+    if (out_gate && glu) LLM_FAIL(-1, "gemm_grouped: an output gate and a glu epilogue exclude one another");
+    if (glu < 0 || glu > 2) LLM_FAIL(-1, "gemm_grouped: glu form %d is not known", glu);
+    if (glu == 1 && limit < 0.f) LLM_FAIL(-1, "gemm_grouped: the clamp's limit %g is negative", (double)limit);
     const int per = dtype == LLM_BF16 ? 8 : 4;
     a.vec_a = !(lda % per) && !(a_group_stride % per) && !(a_offset % per) && !((uintptr_t)A & 15);
     a.vec_w = !(K % per) && !((uintptr_t)W & 15);

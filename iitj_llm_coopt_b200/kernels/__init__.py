@@ -41,7 +41,7 @@ _SIGNATURES = {
     "llm_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "llm_add_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
                         _c_float, _c_int, ctypes.c_longlong, _c_void_p],
-    "llm_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "llm_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "llm_rope_store": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
     "llm_silu_mul": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -101,28 +101,34 @@ _SIGNATURES = {
                            ctypes.c_longlong, _c_void_p, _c_int, _c_int, _c_void_p],
     "llm_retention_headnorm_gate": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                     _c_void_p],
-    "llm_norm_add": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+    "llm_norm_add": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
+                     _c_void_p, _c_void_p],
+    "llm_rmsnorm_rows": [_c_void_p, ctypes.c_longlong, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_int, _c_int, _c_float,
+                         _c_void_p],
+    "llm_glu_act": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_token_side_gate": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "llm_glu_clamped": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
-    "llm_latent_prepare": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p,
+    "llm_latent_prepare": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p,
                            _c_void_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "llm_headnorm_store": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, ctypes.c_longlong, _c_int,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "llm_attention_flat": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+    "llm_attention_flat": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                           _c_void_p],
+                           _c_float, _c_void_p, _c_float, _c_int, _c_void_p],
     "llm_attention_flat_mma_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_longlong],
     "llm_attention_flat_mma_heads_per_block": [_c_int, _c_int],
     "llm_attention_flat_mma_smem": [_c_int, _c_int, _c_int],
-    "llm_attention_flat_mma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
-                               _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
-                               _c_void_p, _c_void_p, _c_void_p],
+    "llm_attention_flat_mma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
+                               _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                               _c_float, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "llm_gemm_grouped_tile_rows": [],
     "llm_gemm_grouped": [_c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p,
                          ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int,
-                         _c_void_p, _c_int, _c_int, _c_float, _c_float, _c_void_p],
-    "llm_route_topk": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
-    "llm_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
-    "llm_gather_rows": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+                         _c_void_p, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p],
+    "llm_route_topk": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                     _c_void_p, _c_void_p],
+    "llm_gather_rows": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "llm_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                         _c_void_p],
     "llm_token_shift": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
@@ -451,15 +457,15 @@ class Kernels:
                    splits, stride, self._stream())
         return out
 
-    def rope_tables(self, positions, inv_freq, cos, sin):
-        """cos[t, i] = cos(positions[t] * inv_freq[i]) and sin likewise, float32 [tokens, rotary_dim/2]."""
+    def rope_tables(self, positions, inv_freq, cos, sin, amplitude: float = 1.0):
+        """cos[t, i] = amplitude * cos(positions[t] * inv_freq[i]) and sin likewise, float32 [tokens, rotary_dim/2]."""
         _check(positions, "rope_tables.positions", torch.int32, 1)
         _check(inv_freq, "rope_tables.inv_freq", torch.float32, 1)
         _check(cos, "rope_tables.cos", torch.float32, 2)
         _check(sin, "rope_tables.sin", torch.float32, 2)
         _need(cos.shape == (positions.shape[0], inv_freq.shape[0]) and sin.shape == cos.shape, "rope_tables: wrong table shape")
         self._call("llm_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), positions.shape[0],
-                   inv_freq.shape[0], self._stream())
+                   inv_freq.shape[0], float(amplitude), self._stream())
         return cos, sin
 
     def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim,
@@ -795,9 +801,10 @@ class Kernels:
         return out
 
     # ---- branch norms, gated feed-forwards with clamps, routed experts ------------------------------------------
-    def norm_add(self, residual, branch, weight, eps, cast_out=None, accumulate: bool = True):
+    def norm_add(self, residual, branch, weight, eps, cast_out=None, accumulate: bool = True, next_weight=None, next_out=None):
         """residual (+)= rmsnorm(branch) * weight with float32 statistics (csrc/branch_norm.cu); `cast_out`: a copy of the new
-        residual in another type (what the next sub-layer reads).  `accumulate` False writes the normed rows instead."""
+        residual in another type (what the next sub-layer reads).  `accumulate` False writes the normed rows instead.
+        With `next_weight` and `next_out` the new residual rows are normed too: next_out = rmsnorm(residual) * next_weight."""
         _check(residual, "norm_add.residual", torch.float32, 2)
         _check(branch, "norm_add.branch", tuple(DTYPE_CODE), 2)
         _check(weight, "norm_add.weight", tuple(DTYPE_CODE), 1)
@@ -806,10 +813,53 @@ class Kernels:
         if cast_out is not None:
             _check(cast_out, "norm_add.cast_out", tuple(DTYPE_CODE), 2)
             _need(cast_out.shape == residual.shape, "norm_add.cast_out: shape differs from residual")
+        typed = cast_out if cast_out is not None else next_out
+        if next_out is not None:
+            _check(next_out, "norm_add.next_out", tuple(DTYPE_CODE), 2)
+            _check(next_weight, "norm_add.next_weight", weight.dtype, 1)
+            _need(next_out.shape == residual.shape and next_weight.shape[0] == width and next_out.dtype == typed.dtype,
+                  "norm_add.next_out: shape or type differs")
+        else:
+            _need(next_weight is None, "norm_add: a second gain without a place for its rows")
         self._call("llm_norm_add", _ptr(residual), _ptr(branch), DTYPE_CODE[branch.dtype], _ptr(weight), DTYPE_CODE[weight.dtype],
-                   _ptr(cast_out), DTYPE_CODE[cast_out.dtype] if cast_out is not None else 0, tokens, width, float(eps),
-                   1 if accumulate else 0, self._stream())
+                   _ptr(cast_out), DTYPE_CODE[typed.dtype] if typed is not None else 0, tokens, width, float(eps),
+                   1 if accumulate else 0, _ptr(next_weight), _ptr(next_out), self._stream())
         return residual
+
+    def rmsnorm_rows(self, x, weight, eps, out):
+        """out[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * weight for rows of the engine's type; x and out may be column ranges of
+        wider matrices (rows with strides of their own, unit stride inside a row)."""
+        _need(x.dim() == 2 and out.dim() == 2 and x.dtype in DTYPE_CODE and out.dtype == x.dtype and x.is_cuda and out.is_cuda,
+              "rmsnorm_rows: two matrices of one of the engine's types on the device")
+        _need(x.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == tuple(x.shape), "rmsnorm_rows: rows must be dense and alike")
+        _check(weight, "rmsnorm_rows.weight", torch.float32, 1)
+        _need(weight.shape[0] == x.shape[1], "rmsnorm_rows.weight: one gain per column")
+        self._call("llm_rmsnorm_rows", x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), _ptr(weight), DTYPE_CODE[x.dtype],
+                   x.shape[0], x.shape[1], float(eps), self._stream())
+        return out
+
+    GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def glu_act(self, gu, act, activation: str):
+        """act = f(gate) * up from gu [T, 2 * inner] (gate columns, then up columns); f is "silu" or "gelu_tanh"."""
+        _check(gu, "glu_act.gu", tuple(DTYPE_CODE), 2)
+        _check(act, "glu_act.act", gu.dtype, 2)
+        _need(gu.shape[1] == 2 * act.shape[1] and gu.shape[0] == act.shape[0], "glu_act: shapes do not fit")
+        _need(activation in self.GLU_ACTIVATIONS, f"glu_act: activation {activation!r} is not known")
+        self._call("llm_glu_act", _ptr(gu), _ptr(act), DTYPE_CODE[gu.dtype], act.shape[0], act.shape[1],
+                   self.GLU_ACTIVATIONS[activation], self._stream())
+        return act
+
+    def token_side_gate(self, gate, table, ids, offset: int, out):
+        """out[t, d] = gelu_tanh(gate[t, d]) * table[ids[t], offset + d] (csrc/token_side.cu)."""
+        _check(gate, "token_side_gate.gate", tuple(DTYPE_CODE), 2)
+        _check(table, "token_side_gate.table", gate.dtype, 2)
+        _check(out, "token_side_gate.out", gate.dtype, 2)
+        _check(ids, "token_side_gate.ids", torch.int32, 1)
+        _need(tuple(out.shape) == tuple(gate.shape) and ids.shape[0] == gate.shape[0], "token_side_gate: shapes do not fit")
+        self._call("llm_token_side_gate", _ptr(gate), _ptr(table), _ptr(ids), _ptr(out), DTYPE_CODE[gate.dtype], gate.shape[0],
+                   gate.shape[1], table.shape[1], int(offset), self._stream())
+        return out
 
     def glu_clamped(self, gu, act, limit: float, slope: float):
         """act = g * sigmoid(slope * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gu [T, 2 * inner]
@@ -821,10 +871,11 @@ class Kernels:
                    float(slope), self._stream())
         return act
 
-    def linear_by_group(self, a, w, out, a_stride: int, out_stride: int, a_offset: int = 0, out_offset: int = 0):
+    def linear_by_group(self, a, w, out, a_stride: int, out_stride: int, a_offset: int = 0, out_offset: int = 0, out_gate=None):
         """One product per group in one launch (csrc/gemm_grouped.cu): with w [groups, n, k] and rows = out.shape[0],
         out[:, out_offset + g * out_stride : ... + n] = A_g . w[g]^T, where row r of A_g starts at element
-        a_offset + g * a_stride + r * a.shape[1] of `a` (a head's slice of a wider row, or a block of rows of its own)."""
+        a_offset + g * a_stride + r * a.shape[1] of `a` (a head's slice of a wider row, or a block of rows of its own).
+        `out_gate`: float32, shaped like `out`; every result number is multiplied by the sigmoid of the number at its place."""
         _check(a, "linear_by_group.a", tuple(DTYPE_CODE), 2)
         _check(w, "linear_by_group.w", a.dtype, 3)
         _check(out, "linear_by_group.out", a.dtype, 2)
@@ -832,22 +883,28 @@ class Kernels:
         rows, lda = out.shape[0], a.shape[1]
         _need(a_offset + (groups - 1) * a_stride + (rows - 1) * lda + k <= a.numel(), "linear_by_group: a is too small")
         _need(out_offset + (groups - 1) * out_stride + n <= out.shape[1], "linear_by_group: out is too narrow")
+        if out_gate is not None:
+            _check(out_gate, "linear_by_group.out_gate", torch.float32, 2)
+            _need(tuple(out_gate.shape) == tuple(out.shape), "linear_by_group.out_gate: shaped like out")
         self._call("llm_gemm_grouped", _ptr(a), lda, int(a_stride), int(a_offset), None, _ptr(w), _ptr(out), out.shape[1],
-                   int(out_stride), int(out_offset), DTYPE_CODE[a.dtype], rows, n, k, groups, None, 0, 0, 0.0, 0.0, self._stream())
+                   int(out_stride), int(out_offset), DTYPE_CODE[a.dtype], rows, n, k, groups, None, 0, 0, 0.0, 0.0, None,
+                   _ptr(out_gate), self._stream())
         return out
 
-    def route_topk(self, scores, correction, chosen, weights):
-        """Router outputs [T, R] float32 -> chosen [T, top] int32 (the largest softmax(scores) + correction, descending)
-        and weights [T, top] float32 (their softmax values); csrc/moe_route.cu."""
+    def route_topk(self, scores, correction, chosen, weights, sigmoid: bool = False):
+        """Router outputs [T, R] float32 -> chosen [T, top] int32 (the largest s + correction, descending; correction None: of
+        s) and weights [T, top] float32 (their s), where s is the softmax over the outputs, or with `sigmoid` each output's
+        sigmoid; csrc/moe_route.cu."""
         _check(scores, "route_topk.scores", torch.float32, 2)
-        _check(correction, "route_topk.correction", torch.float32, 1)
+        if correction is not None:
+            _check(correction, "route_topk.correction", torch.float32, 1)
         _check(chosen, "route_topk.chosen", torch.int32, 2)
         _check(weights, "route_topk.weights", torch.float32, 2)
         tokens, outputs = scores.shape
-        _need(correction.shape[0] == outputs and chosen.shape[0] == tokens and tuple(weights.shape) == tuple(chosen.shape),
-              "route_topk: shapes do not fit")
+        _need((correction is None or correction.shape[0] == outputs) and chosen.shape[0] == tokens and
+              tuple(weights.shape) == tuple(chosen.shape), "route_topk: shapes do not fit")
         self._call("llm_route_topk", _ptr(scores), _ptr(correction), _ptr(chosen), _ptr(weights), tokens, outputs, chosen.shape[1],
-                   self._stream())
+                   1 if sigmoid else 0, self._stream())
 
     def moe_tile_bound(self, rows: int, experts: int) -> int:
         """The most row tiles `moe_plan` can make of `rows` (token, choice) pairs over `experts` experts."""
@@ -858,10 +915,11 @@ class Kernels:
     # kernel's mma.sync tiles reach 150 to 190 TFLOP/s, the dense products 1,000 and more.
     moe_dense_rows = int(os.environ.get("IITJ_MOE_DENSE_ROWS", "2048"))
 
-    def moe_plan(self, chosen, experts: int, source, place, tiles, counts=None):
+    def moe_plan(self, chosen, experts: int, source, place, tiles, counts=None, weights=None, row_weight=None):
         """Sorts the (token, choice) pairs of `chosen` [T, top] by expert on the device: source [T * top] (token of each
         sorted row), place [T * top] (sorted row of each pair, -1 for a choice >= experts), tiles [bound + 1, 4] (count in
-        front, then (expert, first row, rows) records).  Returns what `moe_linear` and `moe_combine` take as `plan`."""
+        front, then (expert, first row, rows) records).  With `weights` [T, top] and `row_weight` [T * top] float32 every
+        pair's weight is also left beside its sorted row.  Returns what `moe_linear` and `moe_combine` take as `plan`."""
         _check(chosen, "moe_plan.chosen", torch.int32, 2)
         for name, t in (("source", source), ("place", place)):
             _check(t, "moe_plan." + name, torch.int32, 1)
@@ -872,42 +930,54 @@ class Kernels:
         if counts is not None:
             _check(counts, "moe_plan.counts", torch.int32, 1)
             _need(counts.shape[0] >= experts, "moe_plan.counts: one per expert")
+        if row_weight is not None:
+            _check(weights, "moe_plan.weights", torch.float32, 2)
+            _check(row_weight, "moe_plan.row_weight", torch.float32, 1)
+            _need(tuple(weights.shape) == tuple(chosen.shape) and row_weight.shape[0] == chosen.numel(), "moe_plan: one weight per pair")
         self._call("llm_moe_plan", _ptr(chosen), chosen.numel(), chosen.shape[1], int(experts),
-                   self.lib.llm_gemm_grouped_tile_rows(), _ptr(source), _ptr(place), _ptr(tiles), bound, _ptr(counts), self._stream())
-        return {"source": source, "place": place, "tiles": tiles, "bound": bound, "counts": counts}
+                   self.lib.llm_gemm_grouped_tile_rows(), _ptr(source), _ptr(place), _ptr(tiles), bound, _ptr(counts),
+                   _ptr(weights) if row_weight is not None else None, _ptr(row_weight), self._stream())
+        return {"source": source, "place": place, "tiles": tiles, "bound": bound, "counts": counts, "row_weight": row_weight}
 
-    def gather_rows(self, x, plan, out):
-        """out[r] = x[plan source of r] for every sorted row r of `plan` (`moe_plan`): the experts' rows side by side."""
+    def gather_rows(self, x, plan, out, weighted: bool = False):
+        """out[r] = x[plan source of r] for every sorted row r of `plan` (`moe_plan`): the experts' rows side by side; `weighted`:
+        times the row's weight (the plan's `row_weight`)."""
         _check(x, "gather_rows.x", tuple(DTYPE_CODE), 2)
         _check(out, "gather_rows.out", x.dtype, 2)
         _need(out.shape[1] == x.shape[1] and out.shape[0] == plan["source"].shape[0], "gather_rows: shapes do not fit")
+        _need(not weighted or plan.get("row_weight") is not None, "gather_rows: the plan holds no row weights")
         self._call("llm_gather_rows", _ptr(x), _ptr(plan["source"]), plan["tiles"].data_ptr() + 4, _ptr(out), DTYPE_CODE[x.dtype],
-                   out.shape[0], x.shape[1], self._stream())
+                   out.shape[0], x.shape[1], _ptr(plan["row_weight"]) if weighted else None, self._stream())
         return out
 
-    def moe_linear(self, a, w, out, plan, gather: bool = False, glu: bool = False, limit: float = 0.0, slope: float = 1.0):
+    def moe_linear(self, a, w, out, plan, gather: bool = False, glu=False, limit: float = 0.0, slope: float = 1.0):
         """out[r] = a[row of r] . w[expert of r]^T for every sorted row r of `plan`; with `gather` a's rows are tokens
-        (read through plan["source"]), else sorted rows.  `glu`: w [E, 2n, k] holds gate rows then up rows and the clamped
-        gate is applied in the epilogue."""
+        (read through plan["source"]), else sorted rows.  `glu`: w [E, 2n, k] holds gate rows then up rows and the gate is
+        applied in the epilogue: True or "clamped" the clamped form (limit, slope), "silu_weighted" silu(w g) * (w u) with
+        the plan's weight w of the row (the expert's product of the row times w)."""
         _check(a, "moe_linear.a", tuple(DTYPE_CODE), 2)
         _check(w, "moe_linear.w", a.dtype, 3)
         _check(out, "moe_linear.out", a.dtype, 2)
         experts, wn, k = w.shape
         n = wn // 2 if glu else wn
         _need(a.shape[1] == k and out.shape[1] == n and out.shape[0] == plan["source"].shape[0], "moe_linear: shapes do not fit")
+        form = 0 if not glu else 2 if glu == "silu_weighted" else 1
+        _need(form != 2 or plan.get("row_weight") is not None, "moe_linear: the plan holds no row weights")
         self._call("llm_gemm_grouped", _ptr(a), a.shape[1], 0, 0, _ptr(plan["source"]) if gather else None, _ptr(w), _ptr(out),
                    out.shape[1], 0, 0, DTYPE_CODE[a.dtype], 0, n, k, experts, _ptr(plan["tiles"]), plan["bound"],
-                   1 if glu else 0, float(limit), float(slope), self._stream())
+                   form, float(limit), float(slope), _ptr(plan["row_weight"]) if form == 2 else None, None, self._stream())
         return out
 
     def moe_combine(self, y, plan, chosen, weights, x, experts: int, out):
-        """out[t] = sum_j weights[t, j] * (y[sorted row of (t, j)], or x[t] where chosen[t, j] >= experts), j in order."""
+        """out[t] = sum_j weights[t, j] * (y[sorted row of (t, j)], or x[t] where chosen[t, j] >= experts), j in order;
+        weights None: all 1."""
         _check(x, "moe_combine.x", tuple(DTYPE_CODE), 2)
         _check(out, "moe_combine.out", x.dtype, 2)
         _check(chosen, "moe_combine.chosen", torch.int32, 2)
-        _check(weights, "moe_combine.weights", torch.float32, 2)
-        _need(out.shape == x.shape and chosen.shape[0] == x.shape[0] and tuple(weights.shape) == tuple(chosen.shape),
-              "moe_combine: shapes do not fit")
+        if weights is not None:
+            _check(weights, "moe_combine.weights", torch.float32, 2)
+        _need(out.shape == x.shape and chosen.shape[0] == x.shape[0] and
+              (weights is None or tuple(weights.shape) == tuple(chosen.shape)), "moe_combine: shapes do not fit")
         if y is not None:
             _check(y, "moe_combine.y", x.dtype, 2)
             _need(y.shape[1] == x.shape[1], "moe_combine.y: width differs")
@@ -925,17 +995,26 @@ class Kernels:
               f"cache: a page of {tuple(cache_layer.shape)} does not hold rows of {kv_heads} heads of {key_dim} (+ {value_dim})")
         return cache_layer.shape[1] // per_token
 
-    def latent_prepare(self, qd, tables, rotary_dim, interleaved, gain, eps, q_out, cache_layer, slots, heads, dim, rot_dim, rank):
+    def latent_prepare(self, qd, tables, rotary_dim, interleaved, gain, eps, q_out, cache_layer, slots, heads, dim, rot_dim, rank,
+                       kv=None):
         """From the fused projection qd [T, heads * (dim + rot_dim) + rank + rot_dim]: the latent part normed (gain [rank]
         float32) and the shared key part rotated, stored together as one cache row per token at `slots` (None: no store);
         every head's rotated query part written to q_out [T, heads * (rank + rot_dim)] behind the place of its absorbed
-        part.  tables = (cos, sin) float32 [T, rotary_dim / 2]; csrc/attention_flat.cu."""
+        part.  tables = (cos, sin) float32 [T, rotary_dim / 2]; csrc/attention_flat.cu.  With `kv` [T, rank + rot_dim] (rows
+        with a stride of their own: columns of another product) qd holds the queries alone."""
         _check(qd, "latent_prepare.qd", tuple(DTYPE_CODE), 2)
         _check(q_out, "latent_prepare.q_out", qd.dtype, 2)
         _check(gain, "latent_prepare.gain", torch.float32, 1)
         tokens = qd.shape[0]
-        _need(qd.shape[1] == heads * (dim + rot_dim) + rank + rot_dim and gain.shape[0] == rank and
-              tuple(q_out.shape) == (tokens, heads * (rank + rot_dim)), "latent_prepare: shapes do not fit")
+        qw = heads * (dim + rot_dim)
+        if kv is None:
+            _need(qd.shape[1] == qw + rank + rot_dim, "latent_prepare.qd: wrong width")
+            kv_ptr, ld_kv = qd.data_ptr() + qw * qd.element_size(), qd.shape[1]
+        else:
+            _need(kv.dim() == 2 and kv.dtype == qd.dtype and kv.is_cuda and kv.stride(1) == 1 and
+                  tuple(kv.shape) == (tokens, rank + rot_dim) and qd.shape[1] == qw, "latent_prepare.kv: [tokens, rank + rot_dim] beside queries alone")
+            kv_ptr, ld_kv = kv.data_ptr(), kv.stride(0)
+        _need(gain.shape[0] == rank and tuple(q_out.shape) == (tokens, heads * (rank + rot_dim)), "latent_prepare: shapes do not fit")
         cos = sin = None
         if rotary_dim:
             cos, sin = tables
@@ -948,7 +1027,7 @@ class Kernels:
             _check(cache_layer, "latent_prepare.cache", qd.dtype, 2)
             _need(slots.shape[0] == tokens, "latent_prepare.slots: one per token")
             page_size, stride = self._flat_page_size(cache_layer, 1, rank + rot_dim, rank, True), cache_layer.shape[1]
-        self._call("llm_latent_prepare", _ptr(qd), qd.shape[1], _ptr(cos), _ptr(sin), int(rotary_dim), 1 if interleaved else 0,
+        self._call("llm_latent_prepare", _ptr(qd), qd.shape[1], kv_ptr, ld_kv, _ptr(cos), _ptr(sin), int(rotary_dim), 1 if interleaved else 0,
                    _ptr(gain), float(eps), _ptr(q_out), _ptr(cache_layer) if slots is not None else None, _ptr(slots), stride,
                    page_size, DTYPE_CODE[qd.dtype], tokens, heads, dim, rot_dim, rank, self._stream())
 
@@ -989,10 +1068,14 @@ class Kernels:
         return max(1, min(32, (resident * self.sm_count) // max(blocks, 1), longest // 256))
 
     def attention_flat(self, q, cache_layer, meta, out, heads, kv_heads, key_dim, value_dim, shared_value: bool = False,
-                       window: int = 0, scale: float = 1.0, gate=None, plan=None):
+                       window: int = 0, scale: float = 1.0, gate=None, plan=None, softcap: float = 0.0, slopes=None,
+                       q_temp=None):
         """Attention of every token's query heads (the leading heads * key_dim numbers of q's rows) over the flat-page
         cache of its request: keys of key_dim, values of value_dim (`shared_value`: the leading value_dim numbers of the key
-        rows), a sliding window (0: all earlier keys), optionally each head's output times sigmoid(gate[t, head])."""
+        rows), a sliding window (0: all earlier keys), optionally the output times sigmoid(gate) (gate [T, heads]: a number
+        per head; [T, heads * value_dim]: per output number).  Score options: `softcap` c > 0 squashes the scaled score to
+        c tanh(s / c); `slopes` [heads] float32 takes slope * (query position - key position) off; `q_temp` = (coef, every)
+        multiplies the query at position p by 1 + coef ln(floor((p + 1) / every) + 1)."""
         _check(q, "attention_flat.q", tuple(DTYPE_CODE), 2)
         _check(cache_layer, "attention_flat.cache", q.dtype, 2)
         _check(out, "attention_flat.out", q.dtype, 2)
@@ -1003,9 +1086,17 @@ class Kernels:
         _check(meta.positions, "attention_flat.positions", torch.int32, 1)
         _need(meta.token_request.shape[0] == tokens and meta.positions.shape[0] == tokens,
               "attention_flat: one token_request and one position per token")
+        gate_cols = 1
         if gate is not None:
             _check(gate, "attention_flat.gate", torch.float32, 2)
-            _need(tuple(gate.shape) == (tokens, heads), "attention_flat.gate: [tokens, heads]")
+            _need(gate.shape[0] == tokens and gate.shape[1] in (heads, heads * value_dim),
+                  "attention_flat.gate: [tokens, heads] or [tokens, heads * value_dim]")
+            gate_cols = gate.shape[1] // heads
+        if slopes is not None:
+            _check(slopes, "attention_flat.slopes", torch.float32, 1)
+            _need(slopes.shape[0] == heads, "attention_flat.slopes: one per head")
+        coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+        _need(every >= 0 and softcap >= 0, "attention_flat: negative softcap or temperature period")
         page_size = self._flat_page_size(cache_layer, kv_heads, key_dim, value_dim, shared_value)
         tiles = plan.device_arrays.get("tiles") if plan is not None else None
         if tiles is not None and q.dtype == torch.bfloat16 and self.flat_mma and q.shape[1] % 8 == 0 and \
@@ -1017,16 +1108,16 @@ class Kernels:
                 part_o = self._scratch("flat.part_o", tokens * heads * splits * value_dim, q.device)
                 part_ml = self._scratch("flat.part_ml", tokens * heads * splits * 2, q.device)
             self._call("llm_attention_flat_mma", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
-                       meta.block_table.shape[1], _ptr(tiles), tiles.shape[0] // 4, _ptr(gate), _ptr(out), out.shape[1], tokens, heads,
-                       kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size, int(window), float(scale), splits,
-                       _ptr(part_o), _ptr(part_ml), self._stream())
+                       meta.block_table.shape[1], _ptr(tiles), tiles.shape[0] // 4, _ptr(gate), gate_cols, _ptr(out), out.shape[1],
+                       tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size, int(window), float(scale),
+                       float(softcap), _ptr(slopes), coef, every, splits, _ptr(part_o), _ptr(part_ml), self._stream())
             if splits > 1:
                 self.launches += 1      # the merge kernel
             return out
         self._call("llm_attention_flat", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
-                   meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(gate), _ptr(out), out.shape[1],
-                   DTYPE_CODE[q.dtype], tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size,
-                   int(window), float(scale), self._stream())
+                   meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(gate), gate_cols, _ptr(out),
+                   out.shape[1], DTYPE_CODE[q.dtype], tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size,
+                   int(window), float(scale), float(softcap), _ptr(slopes), coef, every, self._stream())
         return out
 
     def token_shift(self, x, mu, before, state_slots, token_request, cu_seqlens, out):

@@ -8,14 +8,16 @@ family an arrangement declares for each of its part names and by the `kind` of t
 from __future__ import annotations
 
 from .base import ParamSpec, Part, StepPlan, StepShape
-from .block import Arrangement, BranchNormBlock, BranchNormMixerBlock, PreNormBlock, PreNormMixerBlock
-from .embedding import Embedding, NormedEmbedding, OutputHead
-from .feed_forward import ClampedGLU, RoutedGLU, SwiGLU
+from .block import (Arrangement, BranchNormBlock, BranchNormMixerBlock, PreNormBlock, PreNormMixerBlock, SandwichBlock,
+                    SandwichMixerBlock, SandwichMixerSideBlock, SandwichSideBlock)
+from .embedding import Embedding, NormedEmbedding, OutputHead, SideTableEmbedding
+from .feed_forward import GLU, ClampedGLU, RoutedGLU, SwiGLU
 from .gated_attention import GatedAttention
 from .latent_attention import LatentAttention
 from .mixer import PagedAttention
 from .retention import Retention
 from .talking_attention import TalkingAttention
+from .token_input import GatedTableInput
 from .wkv import WKV
 from .norm import RMSNorm, ScalarGainRMSNorm
 from .position import NoPosition, RotaryEmbedding, rope_inverse_frequencies
@@ -24,15 +26,17 @@ NORMS = {"rmsnorm": RMSNorm, "rmsnorm_scalar": ScalarGainRMSNorm}
 POSITION_ENCODINGS = {"rope": RotaryEmbedding, "none": NoPosition}
 MIXERS = {"attention": PagedAttention, "talking_attention": TalkingAttention, "retention": Retention,
           "latent_attention": LatentAttention, "gated_attention": GatedAttention, "wkv": WKV}
-FEED_FORWARDS = {"swiglu": SwiGLU, "clamped_glu": ClampedGLU, "routed_glu": RoutedGLU}
+FEED_FORWARDS = {"swiglu": SwiGLU, "glu": GLU, "clamped_glu": ClampedGLU, "routed_glu": RoutedGLU}
 ARRANGEMENTS = {"prenorm": PreNormBlock, "prenorm_mixer": PreNormMixerBlock, "branchnorm": BranchNormBlock,
-                "branchnorm_mixer": BranchNormMixerBlock}
-EMBEDDINGS = {"table": Embedding, "table_norm": NormedEmbedding}
+                "branchnorm_mixer": BranchNormMixerBlock, "sandwich": SandwichBlock, "sandwich_mixer": SandwichMixerBlock,
+                "sandwich_side": SandwichSideBlock, "sandwich_mixer_side": SandwichMixerSideBlock}
+EMBEDDINGS = {"table": Embedding, "table_norm": NormedEmbedding, "table_side": SideTableEmbedding}
+TOKEN_INPUTS = {"gated_table": GatedTableInput}
 HEADS = {"linear": OutputHead}
 
 # family name (what an arrangement's PARTS declares for a part name) -> registry
 FAMILIES = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "position": POSITION_ENCODINGS,
-            "embedding": EMBEDDINGS, "head": HEADS}
+            "embedding": EMBEDDINGS, "head": HEADS, "token_input": TOKEN_INPUTS}
 
 
 def register_norm(kind, cls):
@@ -61,3 +65,7 @@ def register_embedding(kind, cls):
 
 def register_head(kind, cls):
     HEADS[kind] = cls
+
+
+def register_token_input(kind, cls):
+    TOKEN_INPUTS[kind] = cls

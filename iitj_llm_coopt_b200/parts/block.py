@@ -116,3 +116,61 @@ class BranchNormMixerBlock(BranchNormBlock):
         x = self._stream(ctx, residual, delta)
         self._add_branch(ctx, residual, self.mixer.forward(ctx, x, call), self.mixer_norm)
         return residual, None
+
+
+class SandwichBlock(Arrangement):
+    """Norms in front of and behind every sub-layer:
+
+        residual += mixer_post_norm(mixer(mixer_norm(residual)))
+        residual += feed_forward_post_norm(feed_forward(feed_forward_norm(residual)))
+        residual += token_input(residual, token)            (arrangements with a "token_input" part)
+
+    The kernel that adds a normed branch also norms the new row for the sub-layer that follows in the same layer
+    (`Kernels.norm_add` with a second gain), and writes the copy of the engine's type that a token input's gate product
+    reads.  A pending delta of an earlier layer is added first; nothing is left over for the next layer."""
+    PARTS = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    CAST = BranchNormBlock.CAST
+
+    def _last_add(self, ctx, residual, branch, norm):
+        """residual += norm(branch), then the layer's token input (if it has one) on the new stream."""
+        side = getattr(self, "token_input", None)
+        cast = None
+        if side is not None and self.mixer.dtype != residual.dtype:
+            cast = ctx.buffer(self.CAST, tuple(residual.shape), self.mixer.dtype)
+        norm.k.norm_add(residual, materialize(branch), norm.weight, norm.eps, cast_out=cast)
+        ctx.shared.pop(self.CAST, None)
+        if side is not None:
+            side.forward(ctx, residual, residual if cast is None else cast)
+
+    def _enter(self, ctx, residual, delta):
+        if delta is not None:
+            residual.add_(delta_for(None, delta))
+            ctx.shared.pop(self.CAST, None)
+        return self.mixer_norm.forward(ctx, residual, None)
+
+    def forward(self, ctx, residual, delta, call):
+        a = self.mixer.forward(ctx, self._enter(ctx, residual, delta), call)
+        post, front = self.mixer_post_norm, self.feed_forward_norm
+        x = ctx.buffer(f"norm.{front.part_name}.out", tuple(residual.shape), self.mixer.dtype)
+        post.k.norm_add(residual, materialize(a), post.weight, post.eps, next_weight=front.weight, next_out=x)
+        self._last_add(ctx, residual, self.feed_forward.forward(ctx, x), self.feed_forward_post_norm)
+        return residual, None
+
+
+class SandwichMixerBlock(SandwichBlock):
+    """The same without a feed-forward."""
+    PARTS = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm"}
+
+    def forward(self, ctx, residual, delta, call):
+        a = self.mixer.forward(ctx, self._enter(ctx, residual, delta), call)
+        self._last_add(ctx, residual, a, self.mixer_post_norm)
+        return residual, None
+
+
+class SandwichSideBlock(SandwichBlock):
+    PARTS = dict(SandwichBlock.PARTS, token_input="token_input")
+
+
+class SandwichMixerSideBlock(SandwichMixerBlock):
+    PARTS = dict(SandwichMixerBlock.PARTS, token_input="token_input")

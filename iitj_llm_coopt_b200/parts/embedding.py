@@ -54,6 +54,25 @@ class NormedEmbedding(Embedding):
         return out
 
 
+class SideTableEmbedding(Embedding):
+    """x = table[token_ids], and a second table [vocab, side_width] (option `side_width`) whose rows the layers' token
+    inputs read by the same ids: it is left in `ctx.shared` for them every step (parts/token_input.py)."""
+
+    def __init__(self, spec, kernels, dtype=None):
+        super().__init__(spec, kernels, dtype)
+        self.side = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        return {"weight": ParamSpec((spec.vocab, spec.width), kind="table"),
+                "side": ParamSpec((spec.vocab, int(dict(spec.options)["side_width"])), kind="table")}
+
+    def forward(self, ctx):
+        from .token_input import SIDE_TABLE
+        ctx.shared[SIDE_TABLE] = self.side
+        return super().forward(ctx)
+
+
 class OutputHead(Part):
     graph_safe = True
 

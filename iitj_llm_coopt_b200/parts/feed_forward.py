@@ -35,6 +35,34 @@ class SwiGLU(Part):
         return self.k.linear(act, self.down, out, defer=True)
 
 
+class GLU(Part):
+    """x -> (f(x Wgate^T) * (x Wup^T)) Wdown^T with f the spec's `activation`: "silu", or "gelu_tanh", the tanh form of
+    gelu, f(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  The silu form runs as `SwiGLU` does (the activation in the
+    product's epilogue); any other as one product and one activation kernel."""
+    graph_safe = True
+
+    def __init__(self, spec, kernels, dtype):
+        if spec.activation not in kernels.GLU_ACTIVATIONS:
+            raise ValueError(f"GLU: activation {spec.activation!r} is not known ({', '.join(kernels.GLU_ACTIVATIONS)})")
+        self.spec, self.k, self.dtype = spec, kernels, dtype
+        self.width, self.inner, self.activation = spec.width, spec.inner, spec.activation
+        self.gate_up = self.down = None
+
+    parameters = SwiGLU.parameters
+
+    def forward(self, ctx, x):
+        t = x.shape[0]
+        act = ctx.buffer("ffn.act", (t, self.inner), self.dtype)
+        if self.activation == "silu":
+            self.k.linear(x, self.gate_up, act, swiglu=True)
+        else:
+            gu = ctx.buffer("ffn.gate_up", (t, 2 * self.inner), self.dtype)
+            self.k.linear(x, self.gate_up, gu)
+            self.k.glu_act(gu, act, self.activation)
+        out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
+        return self.k.linear(act, self.down, out)
+
+
 class ClampedGLU(Part):
     """A gated feed-forward with clamped branches and a sigmoid gate of a given slope:
 
@@ -72,6 +100,12 @@ class RoutedGLU(Part):
         z = x Wrouter^T  (float32),  s = softmax(z) over all router outputs,  chosen = the top entries of s + correction,
         out = sum over the chosen e of s[e] * expert_e(x)            (the weights are not renormalised)
 
+    Options of the spec: `router` = "sigmoid" takes s = sigmoid(z) of every output by itself instead of the softmax;
+    `correction` = False: there is no stored correction and the choice is by s alone; `expert` = "silu" makes the
+    experts plain silu-gated ones, silu(g) * u, instead of the clamped form; `weight_on` = "input" feeds expert e the row
+    s[e] * x and sums the experts' outputs as they are, out = sum expert_e(s[e] * x) (the first product being linear in
+    its row, the weight is applied to gate and up in that product's epilogue, or to the gathered rows).
+
     The last `identity` router outputs stand for experts without tensors that hand their input back (s[e] * x).
     Rows are sorted by expert on the device (`Kernels.moe_plan`), the experts' products run as one grouped product each
     (the first reads its rows through the sorted index, applies the gate in its epilogue), and the chosen experts'
@@ -87,6 +121,16 @@ class RoutedGLU(Part):
         self.experts, self.top = int(spec.experts), int(spec.experts_per_token)
         self.identity = int(spec.option("identity", 0))
         self.limit, self.slope = float(spec.option("limit", 0.0)), float(spec.option("slope", 1.0))
+        self.sigmoid = spec.option("router", "softmax") == "sigmoid"
+        self.has_correction = bool(spec.option("correction", True))
+        self.on_input = spec.option("weight_on", "output") == "input"
+        self.silu = spec.option("expert", "clamped") == "silu"
+        if spec.option("router", "softmax") not in ("softmax", "sigmoid") or spec.option("weight_on", "output") not in ("input", "output"):
+            raise ValueError("routed feed-forward: router is softmax or sigmoid, weight_on is input or output")
+        if self.on_input and (self.identity or not self.silu):
+            raise ValueError("routed feed-forward: weights on the experts' inputs go with plain silu experts and no identity experts")
+        if self.silu and not self.on_input:
+            raise ValueError("routed feed-forward: plain silu experts are served with the weight on their input")
         self.router = self.correction = self.expert_gate_up = self.expert_down = None
         self.prepare_key = f"routed_glu.{self.top}"          # layers with as many choices a token share the step's plan
 
@@ -107,7 +151,9 @@ class RoutedGLU(Part):
     def parameters(cls, spec) -> dict:
         e, ff, w = int(spec.experts), spec.inner, spec.width
         outputs = e + int(spec.option("identity", 0))
-        out = {"router": ParamSpec((outputs, w)), "correction": ParamSpec((outputs,), kind="vector")}
+        out = {"router": ParamSpec((outputs, w))}
+        if spec.option("correction", True):
+            out["correction"] = ParamSpec((outputs,), kind="vector")
         if e:
             out["expert_gate_up"] = ParamSpec((e * 2 * ff, w), pieces=tuple(
                 (f"e{j}.{name}", ff) for j in range(e) for name in ("gate", "up")))
@@ -116,7 +162,8 @@ class RoutedGLU(Part):
 
     def load(self, tensors: dict) -> None:
         super().load(tensors)
-        self.correction = self.correction.float().contiguous()
+        if self.has_correction:
+            self.correction = self.correction.float().contiguous()
 
     def forward(self, ctx, x):
         t = x.shape[0]
@@ -124,7 +171,7 @@ class RoutedGLU(Part):
         self.k.linear(x, self.router, scores)
         chosen = ctx.buffer("moe.chosen", (t, self.top), torch.int32)
         weights = ctx.buffer("moe.weights", (t, self.top), torch.float32)
-        self.k.route_topk(scores, self.correction, chosen, weights)
+        self.k.route_topk(scores, self.correction, chosen, weights, sigmoid=self.sigmoid)
         out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
         plan = y = None
         if self.experts:
@@ -136,12 +183,14 @@ class RoutedGLU(Part):
             plan = self.k.moe_plan(chosen, self.experts, ctx.buffer("moe.source", (rows,), torch.int32),
                                    ctx.buffer("moe.place", (rows,), torch.int32),
                                    ctx.buffer("moe.tiles", (self.k.moe_tile_bound(rows, self.experts) + 1, 4), torch.int32),
-                                   **({"counts": counts} if by_expert else {}))
+                                   **({"counts": counts} if by_expert else {}),
+                                   **({"weights": weights, "row_weight": ctx.buffer("moe.row_weight", (rows,), torch.float32)}
+                                      if self.on_input else {}))
             act = ctx.buffer("moe.act", (rows, self.inner), self.dtype)
             y = ctx.buffer("moe.y", (rows, self.width), self.dtype)
             if by_expert:
                 sizes = counts.tolist()                      # the one read of the host in this layer
-                xs = self.k.gather_rows(x, plan, ctx.buffer("moe.rows", (rows, self.width), self.dtype))
+                xs = self.k.gather_rows(x, plan, ctx.buffer("moe.rows", (rows, self.width), self.dtype), weighted=self.on_input)
                 gu = ctx.buffer("moe.gate_up", (rows, 2 * self.inner), self.dtype)
                 live, spans = 0, []
                 for n in sizes:
@@ -150,12 +199,15 @@ class RoutedGLU(Part):
                 for e, (lo, hi) in enumerate(spans):
                     if hi > lo:
                         self.k.linear(xs[lo:hi], w1[e], gu[lo:hi])
-                if live:
+                if live and self.silu:
+                    self.k.glu_act(gu[:live], act[:live], "silu")
+                elif live:
                     self.k.glu_clamped(gu[:live], act[:live], self.limit, self.slope)
                 for e, (lo, hi) in enumerate(spans):
                     if hi > lo:
                         self.k.linear(act[lo:hi], w2[e], y[lo:hi])
             else:
-                self.k.moe_linear(x, w1, act, plan, gather=True, glu=True, limit=self.limit, slope=self.slope)
+                self.k.moe_linear(x, w1, act, plan, gather=True, glu="silu_weighted" if self.silu else True, limit=self.limit,
+                                  slope=self.slope)
                 self.k.moe_linear(act, w2, y, plan)
-        return self.k.moe_combine(y, plan, chosen, weights, x, self.experts, out)
+        return self.k.moe_combine(y, plan, chosen, None if self.on_input else weights, x, self.experts, out)

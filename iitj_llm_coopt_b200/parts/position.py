@@ -7,6 +7,11 @@ angle position * inv_freq and its sine and cosine are evaluated in float32 insid
 kernel for every token, so no table of max_position rows exists and none is rounded to
 the model's type.
 
+A scaling law of type "yarn" (factor, original, fast, slow) blends every pair's frequency f_i with f_i / factor along
+a ramp over the pair index i: with turns(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(turns(fast)), 0),
+hi = min(ceil(turns(slow)), rotary_dim - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency becomes
+f_i / factor * r_i + f_i * (1 - r_i), and sine and cosine are both multiplied by 0.1 ln(factor) + 1 (`rope_amplitude`).
+
 `NoPosition` leaves queries and keys as they are and only stores keys and values.
 """
 from __future__ import annotations
@@ -34,6 +39,30 @@ def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling: dict | None
     return torch.where(medium, smoothed, scaled).float()
 
 
+def yarn_frequencies(rotary_dim: int, theta: float, scaling: dict) -> torch.Tensor:
+    """float32 [rotary_dim/2]: the blended frequencies of the "yarn" law (module text), computed in double precision."""
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def turns(t: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(turns(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(turns(float(scaling["slow"]))), rotary_dim - 1)
+    out = []
+    for i in range(rotary_dim // 2):
+        f = theta ** (-2.0 * i / rotary_dim)
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / factor * ramp + f * (1.0 - ramp))
+    return torch.tensor(out, dtype=torch.float64).float()
+
+
+def rope_amplitude(scaling: dict | None) -> float:
+    """The factor on sine and cosine alike that a scaling law asks for (1 for none and for llama3)."""
+    if scaling and scaling.get("type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 class RotaryEmbedding(Part):
     graph_safe = True
     takes_partial_sums = True     # encode_and_store adds the k-split parts of the qkv product as it reads them
@@ -41,7 +70,12 @@ class RotaryEmbedding(Part):
     def __init__(self, spec, kernels, dtype, device="cuda"):
         self.spec, self.k = spec, kernels
         self.head_dim, self.rotary_dim = spec.head_dim, spec.rotary_dim
-        self.inv_freq = rope_inverse_frequencies(spec.rotary_dim, spec.theta, spec.scaling_dict()).to(device)
+        scaling = spec.scaling_dict()
+        if scaling.get("type") == "yarn":
+            self.inv_freq = yarn_frequencies(spec.rotary_dim, spec.theta, scaling).to(device)
+        else:
+            self.inv_freq = rope_inverse_frequencies(spec.rotary_dim, spec.theta, scaling).to(device)
+        self.amplitude = rope_amplitude(scaling)
 
     def tables(self, ctx):
         """cos and sin of this step's positions, computed by the first layer that asks and shared by
@@ -53,7 +87,10 @@ class RotaryEmbedding(Part):
             name = f"rope.{hash(self.spec) & 0xffffffff:x}"
             cos = ctx.buffer(name + ".cos", (ctx.num_tokens, half), torch.float32)
             sin = ctx.buffer(name + ".sin", (ctx.num_tokens, half), torch.float32)
-            tabs = ctx.shared[key] = self.k.rope_tables(ctx.positions, self.inv_freq, cos, sin)
+            if self.amplitude != 1.0:
+                tabs = ctx.shared[key] = self.k.rope_tables(ctx.positions, self.inv_freq, cos, sin, amplitude=self.amplitude)
+            else:
+                tabs = ctx.shared[key] = self.k.rope_tables(ctx.positions, self.inv_freq, cos, sin)
         return tabs
 
     def encode_and_store(self, ctx, qkv, cache_view, slots, heads, kv_heads):
@@ -63,7 +100,7 @@ class RotaryEmbedding(Part):
     def decode_tables(self, ctx):
         """(cos, sin) for a mixer whose decode kernel rotates and stores by itself, or None if this encoding
         cannot be handed over like that (only part of the head is rotated)."""
-        return self.tables(ctx) if self.rotary_dim == self.head_dim else None
+        return self.tables(ctx) if self.rotary_dim == self.head_dim and self.amplitude == 1.0 else None
 
 
 class NoPosition(Part):
