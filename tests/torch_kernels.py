@@ -195,6 +195,27 @@ def ref_norm_add(residual, branch, weight, eps, accumulate=True):
     return residual.float() + y if accumulate else y
 
 
+def ref_gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+def ref_glu_act(gu, activation):
+    """f(gate) * up of a [T, 2 * inner] product, f silu or the tanh form of gelu; float32."""
+    n = gu.shape[1] // 2
+    g, u = gu[:, :n].float(), gu[:, n:].float()
+    return (ref_gelu_tanh(g) if activation == "gelu_tanh" else g * torch.sigmoid(g)) * u
+
+
+def ref_rmsnorm_rows(x, weight, eps):
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+
+
+def ref_token_side_gate(gate, table, ids, offset):
+    d = gate.shape[1]
+    return ref_gelu_tanh(gate.float()) * table[ids.long()][:, offset:offset + d].float()
+
+
 def ref_glu_clamped(gu, limit, slope):
     n = gu.shape[1] // 2
     g = torch.clamp(gu[:, :n].float(), max=limit)
@@ -220,12 +241,13 @@ def ref_rotate(v, cos, sin, dims, interleaved):
     return out
 
 
-def ref_latent_prepare(qd, cos, sin, rotary_dim, interleaved, gain, eps, heads, dim, rot_dim, rank):
-    """Returns (rotated query parts [T, H, rot_dim], cache rows [T, rank + rot_dim]) in float32."""
+def ref_latent_prepare(qd, cos, sin, rotary_dim, interleaved, gain, eps, heads, dim, rot_dim, rank, kv=None):
+    """Returns (rotated query parts [T, H, rot_dim], cache rows [T, rank + rot_dim]) in float32.  `kv`: the latent and shared
+    key columns when qd holds the queries alone."""
     T = qd.shape[0]
     x = qd.float()
     q = x[:, :heads * (dim + rot_dim)].view(T, heads, dim + rot_dim)
-    d = x[:, heads * (dim + rot_dim):]
+    d = x[:, heads * (dim + rot_dim):] if kv is None else kv.float()
     lat = d[:, :rank]
     lat = lat * torch.rsqrt(lat.pow(2).mean(-1, keepdim=True) + eps) * gain.float()
     kr = ref_rotate(d[:, rank:].reshape(T, 1, rot_dim), cos, sin, rotary_dim, interleaved)[:, 0]
@@ -256,8 +278,10 @@ def flat_planes(cache, kv_heads, key_dim, value_dim, shared_value):
 
 
 def ref_attention_flat(q, q_stride_heads, cache, block_table, token_request, positions, heads, kv_heads, key_dim, value_dim,
-                       shared_value, window, scale, gate=None):
-    """q [T, >= heads * key_dim] (query heads first); returns [T, heads * value_dim] float32."""
+                       shared_value, window, scale, gate=None, softcap=0.0, slopes=None, q_temp=None):
+    """q [T, >= heads * key_dim] (query heads first); returns [T, heads * value_dim] float32.  gate [T, heads] or
+    [T, heads * value_dim]; score options: tanh squashing at `softcap`, `slopes` [heads] times the distance taken off,
+    `q_temp` (coef, every) the query's growth with the logarithm of its position."""
     T = q.shape[0]
     kplane, vplane, ps = flat_planes(cache, kv_heads, key_dim, value_dim, shared_value)
     group = heads // kv_heads
@@ -271,17 +295,24 @@ def ref_attention_flat(q, q_stride_heads, cache, block_table, token_request, pos
         k = kplane[pages, :, offs, :].float().repeat_interleave(group, dim=1)
         v = vplane[pages, :, offs, :].float().repeat_interleave(group, dim=1)
         qt = q[t, :heads * key_dim].float().view(heads, key_dim)
-        p = torch.softmax(torch.einsum("hd,nhd->hn", qt, k) * scale, dim=-1)
+        s = torch.einsum("hd,nhd->hn", qt, k) * scale
+        if q_temp:
+            s = s * (1.0 + q_temp[0] * math.log((pos + 1) // q_temp[1] + 1.0))
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if slopes is not None:
+            s = s - slopes.float().view(heads, 1) * (pos - idx).float().view(1, -1)
+        p = torch.softmax(s, dim=-1)
         o = torch.einsum("hn,nhv->hv", p, v)
         if gate is not None:
-            o = o * torch.sigmoid(gate[t].float()).view(heads, 1)
+            o = o * torch.sigmoid(gate[t].float()).view(heads, -1)
         out[t] = o
     return out.view(T, heads * value_dim)
 
 
-def ref_route_topk(scores, correction, top):
-    s = torch.softmax(scores.float(), dim=-1)
-    chosen = torch.topk(s + correction.float(), top, dim=-1).indices
+def ref_route_topk(scores, correction, top, sigmoid=False):
+    s = torch.sigmoid(scores.float()) if sigmoid else torch.softmax(scores.float(), dim=-1)
+    chosen = torch.topk(s + correction.float() if correction is not None else s, top, dim=-1).indices
     return chosen.to(torch.int32), torch.gather(s, 1, chosen)
 
 
@@ -377,10 +408,10 @@ class TorchKernels:
         out.copy_(y)
         return out
 
-    def rope_tables(self, positions, inv_freq, cos, sin):
+    def rope_tables(self, positions, inv_freq, cos, sin, amplitude=1.0):
         ang = positions.float().unsqueeze(1) * inv_freq.float().unsqueeze(0)
-        cos.copy_(ang.cos())
-        sin.copy_(ang.sin())
+        cos.copy_(ang.cos() * amplitude)
+        sin.copy_(ang.sin() * amplitude)
         return cos, sin
 
     def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim, tables=None):
@@ -445,28 +476,47 @@ class TorchKernels:
     # ---- the Rodapel family ---------------------------------------------------------------------------------
     MOE_TILE_ROWS = 64
 
-    def norm_add(self, residual, branch, weight, eps, cast_out=None, accumulate=True):
+    def norm_add(self, residual, branch, weight, eps, cast_out=None, accumulate=True, next_weight=None, next_out=None):
         residual.copy_(ref_norm_add(residual, branch, weight, eps, accumulate))
         if cast_out is not None:
             cast_out.copy_(residual)
+        if next_out is not None:
+            next_out.copy_(ref_rmsnorm_rows(residual, next_weight, eps))
         return residual
+
+    def rmsnorm_rows(self, x, weight, eps, out):
+        out.copy_(ref_rmsnorm_rows(x, weight, eps))
+        return out
+
+    GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def glu_act(self, gu, act, activation):
+        act.copy_(ref_glu_act(gu, activation))
+        return act
+
+    def token_side_gate(self, gate, table, ids, offset, out):
+        out.copy_(ref_token_side_gate(gate, table, ids, offset))
+        return out
 
     def glu_clamped(self, gu, act, limit, slope):
         act.copy_(ref_glu_clamped(gu, limit, slope))
         return act
 
-    def linear_by_group(self, a, w, out, a_stride, out_stride, a_offset=0, out_offset=0):
+    def linear_by_group(self, a, w, out, a_stride, out_stride, a_offset=0, out_offset=0, out_gate=None):
         groups, n, k = w.shape
         rows, lda = out.shape[0], a.shape[1]
         flat = a.reshape(-1)
         for g in range(groups):
             ag = torch.as_strided(flat, (rows, k), (lda, 1), a_offset + g * a_stride)
-            out[:, out_offset + g * out_stride:out_offset + g * out_stride + n] = ag.float() @ w[g].float().t()
+            y = ag.float() @ w[g].float().t()
+            if out_gate is not None:
+                y = y * torch.sigmoid(out_gate[:, out_offset + g * out_stride:out_offset + g * out_stride + n])
+            out[:, out_offset + g * out_stride:out_offset + g * out_stride + n] = y
         return out
 
-    def latent_prepare(self, qd, tables, rotary_dim, interleaved, gain, eps, q_out, cache, slots, heads, dim, rot_dim, rank):
+    def latent_prepare(self, qd, tables, rotary_dim, interleaved, gain, eps, q_out, cache, slots, heads, dim, rot_dim, rank, kv=None):
         cos, sin = tables if tables is not None else (None, None)
-        qr, rows = ref_latent_prepare(qd, cos, sin, rotary_dim, interleaved, gain, eps, heads, dim, rot_dim, rank)
+        qr, rows = ref_latent_prepare(qd, cos, sin, rotary_dim, interleaved, gain, eps, heads, dim, rot_dim, rank, kv)
         T = qd.shape[0]
         q_out.view(T, heads, rank + rot_dim)[..., rank:] = qr.to(q_out.dtype)
         if slots is not None:
@@ -487,20 +537,20 @@ class TorchKernels:
                 vplane[p, :, o, :] = v[t].to(cache.dtype)
 
     def attention_flat(self, q, cache, meta, out, heads, kv_heads, key_dim, value_dim, shared_value=False, window=0, scale=1.0,
-                       gate=None, plan=None):
+                       gate=None, plan=None, softcap=0.0, slopes=None, q_temp=None):
         out.copy_(ref_attention_flat(q, None, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
-                                     key_dim, value_dim, shared_value, window, scale, gate))
+                                     key_dim, value_dim, shared_value, window, scale, gate, softcap, slopes, q_temp))
         return out
 
-    def route_topk(self, scores, correction, chosen, weights):
-        c, w = ref_route_topk(scores, correction, chosen.shape[1])
+    def route_topk(self, scores, correction, chosen, weights, sigmoid=False):
+        c, w = ref_route_topk(scores, correction, chosen.shape[1], sigmoid)
         chosen.copy_(c)
         weights.copy_(w)
 
     def moe_tile_bound(self, rows, experts):
         return -(-rows // self.MOE_TILE_ROWS) + experts
 
-    def moe_plan(self, chosen, experts, source, place, tiles, counts=None):
+    def moe_plan(self, chosen, experts, source, place, tiles, counts=None, weights=None, row_weight=None):
         """Rows (token, choice) sorted by expert: source[r] = token of sorted row r, place[token * top + j] = its sorted row
         (-1 for an expert without tensors), tiles[0, 0] = count, tiles[1 + i] = (expert, first row, rows, 0)."""
         top = chosen.shape[1]
@@ -511,6 +561,8 @@ class TorchKernels:
         for r, (e, i) in enumerate(order):
             source[r] = i // top
             place[i] = r
+            if row_weight is not None:
+                row_weight[r] = weights.reshape(-1)[i]
         for e in range(experts):
             n = sum(1 for x, _ in order if x == e)
             for s in range(0, n, self.MOE_TILE_ROWS):
@@ -524,13 +576,14 @@ class TorchKernels:
         tiles[0, 1] = len(order)
         for i, rec in enumerate(recs):
             tiles[1 + i] = torch.tensor(rec, dtype=torch.int32)
-        return {"source": source, "place": place, "tiles": tiles, "rows": len(order), "counts": counts}
+        return {"source": source, "place": place, "tiles": tiles, "rows": len(order), "counts": counts, "row_weight": row_weight}
 
     moe_dense_rows = 40          # small, so that the CPU tests take the expert-by-expert way for their longer portions
 
-    def gather_rows(self, x, plan, out):
+    def gather_rows(self, x, plan, out, weighted=False):
         n = plan["rows"]
-        out[:n] = x[plan["source"][:n].long()]
+        rows = x[plan["source"][:n].long()]
+        out[:n] = rows.float() * plan["row_weight"][:n].unsqueeze(1) if weighted else rows
         return out
 
     def moe_linear(self, a, w, out, plan, gather=False, glu=False, limit=0.0, slope=1.0):
@@ -539,7 +592,11 @@ class TorchKernels:
             e, r0, n, _ = (int(v) for v in tiles[1 + i])
             rows = plan["source"][r0:r0 + n].long() if gather else torch.arange(r0, r0 + n)
             y = a[rows].float() @ w[e].float().t()
-            out[r0:r0 + n] = ref_glu_clamped(y, limit, slope) if glu else y
+            if glu == "silu_weighted":
+                y = ref_glu_act(y * plan["row_weight"][r0:r0 + n].unsqueeze(1), "silu")
+            elif glu:
+                y = ref_glu_clamped(y, limit, slope)
+            out[r0:r0 + n] = y
         return out
 
     def moe_combine(self, y, plan, chosen, weights, x, experts, out):
@@ -549,7 +606,7 @@ class TorchKernels:
             for j in range(top):
                 e = int(chosen[t, j])
                 row = x[t].float() if e >= experts else y[int(plan["place"][t * top + j])].float()
-                acc[t] += float(weights[t, j]) * row
+                acc[t] += (float(weights[t, j]) if weights is not None else 1.0) * row
         out.copy_(acc)
         return out
 
