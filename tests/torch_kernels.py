@@ -528,7 +528,8 @@ class TorchKernels:
     def headnorm_store(self, qkv, q_gain, k_gain, eps, cache, slots, heads, kv_heads, dim, vdim):
         q, k, v = ref_headnorm(qkv, q_gain, k_gain, eps, heads, kv_heads, dim, vdim)
         T = qkv.shape[0]
-        qkv[:, :heads * dim] = q.reshape(T, -1).to(qkv.dtype)
+        if q_gain is not None:                      # without gains the queries stay as the product left them
+            qkv[:, :heads * dim] = q.reshape(T, -1).to(qkv.dtype)
         if slots is not None:
             kplane, vplane, ps = flat_planes(cache, kv_heads, dim, vdim, False)
             for t in range(T):
