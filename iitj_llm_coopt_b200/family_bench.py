@@ -354,6 +354,183 @@ def _kernels_alone_rodapel(cfg, llama, tokens, batch, context, hbm_gbs, flush):
     return out
 
 
+def _kernels_alone_fomerax(cfg, rod, tokens, batch, context, hbm_gbs, flush):
+    """The kernels and kernel options that Fomerax brought, alone at the shapes of a `tokens`-token prompt and of a decode
+    step of `batch` requests, each beside the like kernel as Rodapel runs it at the same shape (the same kernel without
+    the option, mostly): microseconds, the bytes that must move and the fraction of the copy bandwidth that is, or for the
+    arithmetic-bound prompt attention the TFLOP/s of the scores and sums."""
+    import torch
+
+    from . import kernels as _k
+    from .parts.base import StepShape
+    from .parts.flat_tiles import plan_flat_tiles
+    K = _k.load()
+    dev, bf = "cuda", torch.bfloat16
+    att = next(l["mixer"] for l in cfg["layers"] if l["type"] == "attention")
+    lat = next(l["mixer"] for l in cfg["layers"] if l["type"] == "latent_attention")
+    moe = next(l["mlp"] for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
+    dense = next(l["mlp"] for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "dense")
+    width, side = cfg["width"], cfg["token_side"]["dim"]
+    H, G, D, V = att["heads"], att["kv_heads"], att["dim"], att["vdim"]
+    LH, LD, LR, LC, LQ, LV, window = lat["heads"], lat["dim"], lat["rot_dim"], lat["kv_rank"], lat["q_rank"], lat["vdim"], lat["mask"]["size"]
+    page = 16
+    out = []
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def record(name, us, nbytes=None, flops=None, like=None):
+        r = {"kernel": name, "us": round(us, 2)}
+        if nbytes is not None:
+            r.update(mbytes=round(nbytes / 1e6, 2), frac_of_copy_bandwidth=round(nbytes / (us * 1e-6) / (hbm_gbs * 1e9), 3))
+        if flops is not None:
+            r.update(tflops=round(flops / (us * 1e-6) / 1e12, 1))
+        if like:
+            r["like"] = like
+        out.append(r)
+
+    for label, T, B, per in (("prefill", tokens, 1, tokens), ("decode", batch, batch, 1)):
+        ctx_len = per if label == "prefill" else context
+        pages_per = -(-ctx_len // page)
+        treq = [b for b in range(B) for _ in range(per)]
+        pos = [ctx_len - per + i for _ in range(B) for i in range(per)]
+        table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+        slots = i32([int(table[b, p // page]) * page + p % page for b, p in zip(treq, pos)])
+        meta = SimpleNamespace(block_table=table, token_request=i32(treq), positions=i32(pos), query_lens=[per] * B,
+                               seq_lens_host=[ctx_len] * B, attention_plan=None)
+
+        def plan_for(heads, kv_heads, key_dim, value_dim, win, shared=False):
+            plan = plan_flat_tiles(K, StepShape([per] * B, [ctx_len] * B, T, label == "decode", False, dev), heads, kv_heads,
+                                   key_dim, value_dim, win, shared_value=shared)
+            plan.bind({"tiles": i32(plan.arrays["tiles"])})
+            return plan
+        causal = sum(p + 1 for p in pos)
+        seen = sum(min(p + 1, window) for p in pos)
+        # --- biased attention over all earlier keys: cap, distance bias, temperature, a gate per output number; beside the plain
+        #     scores with a gate per head
+        qkv = torch.randn(T, H * D + G * (D + V), device=dev).to(bf)
+        cache = (torch.randn(B * pages_per + 1, G * page * (D + V), device=dev) * 0.5).to(bf)
+        ao = torch.empty(T, H * V, device=dev, dtype=bf)
+        egate, hgate = torch.randn(T, H * V, device=dev), torch.randn(T, H, device=dev)
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+        plan = plan_for(H, G, D, V, 0)
+        extras = dict(softcap=float(att.get("softcap") or 0.0), slopes=slopes,
+                      q_temp=(att["q_temp"]["coef"], att["q_temp"]["every"]) if att.get("q_temp") else None)
+        for name, kw, like in ((f"attention_flat, cap + bias + temperature + gate per number ({label})", dict(gate=egate, **extras), f"attention_flat, plain scores ({label})"),
+                               (f"attention_flat, plain scores ({label})", dict(gate=hgate), None)):
+            us = 1e3 * _timed(lambda: K.attention_flat(qkv, cache, meta, ao, H, G, D, V, scale=D ** -0.5, plan=plan, **kw), 5, 3, flush)
+            if label == "decode":
+                record(name, us, nbytes=B * ctx_len * G * (D + V) * 2, like=like)
+            else:
+                record(name, us, flops=2 * causal * H * (D + V), like=like)
+        # --- latent attention: the queries' latent normed, the latent rows beside queries of another product, the window
+        row = LC + LR
+        down = torch.randn(T, LQ + row, device=dev).to(bf)
+        cq = torch.empty(T, LQ, device=dev, dtype=bf)
+        qgain = torch.ones(LQ, device=dev)
+        us = 1e3 * _timed(lambda: K.rmsnorm_rows(down[:, :LQ], qgain, 1e-6, cq), 10, 3, flush)
+        record(f"rmsnorm_rows, the queries' latent ({label})", us, nbytes=T * LQ * 2 * 2, like="norm_add")
+        qd = torch.randn(T, LH * (LD + LR), device=dev).to(bf)
+        qd_all = torch.randn(T, LH * (LD + LR) + row, device=dev).to(bf)
+        lat_cache = (torch.randn(B * pages_per + 1, page * row, device=dev) * 0.5).to(bf)
+        ang = torch.tensor(pos, device=dev).float().unsqueeze(1) * (1.0 / 1e4 ** (torch.arange(LR // 2, device=dev).float() / (LR // 2)))
+        tabs = (ang.cos().contiguous(), ang.sin().contiguous())
+        lgain = torch.ones(LC, device=dev)
+        qa = torch.empty(T, LH * row, device=dev, dtype=bf)
+        moved = T * (LH * (LD + 2 * LR) + 2 * row) * 2
+        us = 1e3 * _timed(lambda: K.latent_prepare(qd, tabs, LR, True, lgain, 1e-6, qa, lat_cache, slots, LH, LD, LR, LC, kv=down[:, LQ:]), 10, 3, flush)
+        record(f"latent_prepare, rows of another product ({label})", us, nbytes=moved, like=f"latent_prepare ({label})")
+        us = 1e3 * _timed(lambda: K.latent_prepare(qd_all, tabs, LR, True, lgain, 1e-6, qa, lat_cache, slots, LH, LD, LR, LC), 10, 3, flush)
+        record(f"latent_prepare ({label})", us, nbytes=moved)
+        lo2 = torch.empty(T, LH * LC, device=dev, dtype=bf)
+        for win, name, like in ((window, f"attention_flat, latent rows, window {window} ({label})", f"attention_flat, latent rows ({label})"),
+                                (0, f"attention_flat, latent rows ({label})", None)):
+            lplan = plan_for(LH, 1, row, LC, win, shared=True)
+            us = 1e3 * _timed(lambda: K.attention_flat(qa, lat_cache, meta, lo2, LH, 1, row, LC, shared_value=True, scale=0.07, window=win, plan=lplan), 3, 3, flush)
+            keys = seen if win else causal
+            if label == "decode":
+                record(name, us, nbytes=B * (min(ctx_len, win) if win else ctx_len) * row * 2, like=like)
+            else:
+                record(name, us, flops=2 * keys * LH * (row + LC), like=like)
+        uv = (torch.randn(LH, LV, LC, device=dev) * LC ** -0.5).to(bf)
+        vo = torch.empty(T, LH * LV, device=dev, dtype=bf)
+        lgate = torch.randn(T, LH * LV, device=dev)
+        nb = (T * LH * (LC + LV) + LH * LC * LV) * 2
+        us = 1e3 * _timed(lambda: K.linear_by_group(lo2, uv, vo, a_stride=LC, out_stride=LV, out_gate=lgate), 10, 3, flush)
+        record(f"values' product per head with the gate ({label})", us, nbytes=nb + T * LH * LV * 4, flops=2 * T * LH * LV * LC,
+               like=f"values' product per head ({label})")
+        us = 1e3 * _timed(lambda: K.linear_by_group(lo2, uv, vo, a_stride=LC, out_stride=LV), 10, 3, flush)
+        record(f"values' product per head ({label})", us, nbytes=nb, flops=2 * T * LH * LV * LC)
+        # --- norms on both sides: the branch norm that also norms the new row, beside the branch norm alone
+        res = torch.randn(T, width, device=dev)
+        branch = torch.randn(T, width, device=dev).to(bf)
+        nw = torch.ones(width, device=dev)
+        cast, nxt = torch.empty(T, width, device=dev, dtype=bf), torch.empty(T, width, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.norm_add(res, branch, nw, 1e-6, next_weight=nw, next_out=nxt), 10, 3, flush)
+        record(f"norm_add with the next norm ({label})", us, nbytes=T * width * (2 + 4 + 4 + 2), like=f"norm_add ({label})")
+        us = 1e3 * _timed(lambda: K.norm_add(res, branch, nw, 1e-6, cast_out=cast), 10, 3, flush)
+        record(f"norm_add ({label})", us, nbytes=T * width * (2 + 4 + 4 + 2))
+        # --- the token input's gate
+        z = torch.randn(T, side, device=dev).to(bf)
+        n_layers = len(cfg["layers"])
+        stable = torch.randn(4096, n_layers * side, device=dev).to(bf)
+        ids = torch.randint(0, 4096, (T,), dtype=torch.int32, device=dev)
+        g = torch.empty(T, side, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.token_side_gate(z, stable, ids, side, g), 10, 3, flush)
+        record(f"token_side_gate ({label})", us, nbytes=T * side * 2 * 3, like=f"glu_clamped ({label})")
+        # --- the dense feed-forward's activation, beside the clamped one
+        inner = dense["ff"]
+        gu = torch.randn(T, 2 * inner, device=dev).to(bf)
+        act = torch.empty(T, inner, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.glu_act(gu, act, "gelu_tanh"), 10, 3, flush)
+        record(f"glu_act gelu_tanh ({label})", us, nbytes=T * inner * 2 * 3, like=f"glu_clamped ({label})")
+        us = 1e3 * _timed(lambda: K.glu_clamped(gu, act, 7.0, 1.702), 10, 3, flush)
+        record(f"glu_clamped ({label})", us, nbytes=T * inner * 2 * 3)
+        x = torch.randn(T, width, device=dev).to(bf)
+        wg = (torch.randn(2 * inner, width, device=dev) * width ** -0.5).to(bf)
+        us = 1e3 * _timed(lambda: K.linear(x, wg, gu), 5, 3, flush)
+        record(f"gate/up product ({label})", us, nbytes=wg.numel() * 2 + T * (width + 2 * inner) * 2, flops=4 * T * inner * width)
+        # --- routed experts: choice by sigmoid, the plan with row weights, the first product with weighted silu, the plain sum
+        E, top, ff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]
+        scores = torch.randn(T, E, device=dev)
+        corr = torch.zeros(E, device=dev)
+        chosen = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, top, device=dev)
+        us = 1e3 * _timed(lambda: K.route_topk(scores, None, chosen, wts, sigmoid=True), 10, 3, flush)
+        record(f"route_topk, sigmoid ({label})", us, like=f"route_topk, softmax ({label})")
+        us = 1e3 * _timed(lambda: K.route_topk(scores, corr, chosen, wts), 10, 3, flush)
+        record(f"route_topk, softmax ({label})", us)
+        K.route_topk(scores, None, chosen, wts, sigmoid=True)
+        rows = T * top
+        bufs = (torch.zeros(rows, dtype=torch.int32, device=dev), torch.zeros(rows, dtype=torch.int32, device=dev),
+                torch.zeros(K.moe_tile_bound(rows, E) + 1, 4, dtype=torch.int32, device=dev))
+        rw = torch.zeros(rows, device=dev)
+        us = 1e3 * _timed(lambda: K.moe_plan(chosen, E, *bufs, weights=wts, row_weight=rw), 10, 3, flush)
+        record(f"moe_plan with row weights ({label})", us, like=f"moe_plan ({label})")
+        us = 1e3 * _timed(lambda: K.moe_plan(chosen, E, *bufs), 10, 3, flush)
+        record(f"moe_plan ({label})", us)
+        plan_w = K.moe_plan(chosen, E, *bufs, weights=wts, row_weight=rw)
+        w1 = (torch.randn(E, 2 * ff, width, device=dev) * width ** -0.5).to(bf)
+        w2 = (torch.randn(E, width, ff, device=dev) * ff ** -0.5).to(bf)
+        eact = torch.empty(rows, ff, device=dev, dtype=bf)
+        y = torch.empty(rows, width, device=dev, dtype=bf)
+        live = int(plan_w["tiles"][0, 1])
+        nb = w1.numel() * 2 + live * (width + ff) * 2
+        us = 1e3 * _timed(lambda: K.moe_linear(x, w1, eact, plan_w, gather=True, glu="silu_weighted"), 5, 3, flush)
+        record(f"experts' gate/up product, weighted silu ({label})", us, nbytes=nb, flops=4 * live * ff * width,
+               like=f"experts' gate/up product, clamped gate ({label})")
+        us = 1e3 * _timed(lambda: K.moe_linear(x, w1, eact, plan_w, gather=True, glu=True, limit=7.0, slope=1.702), 5, 3, flush)
+        record(f"experts' gate/up product, clamped gate ({label})", us, nbytes=nb, flops=4 * live * ff * width)
+        us = 1e3 * _timed(lambda: K.moe_linear(eact, w2, y, plan_w), 5, 3, flush)
+        record(f"experts' down product ({label})", us, nbytes=w2.numel() * 2 + live * (width + ff) * 2, flops=2 * live * ff * width)
+        mo = torch.empty(T, width, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.moe_combine(y, plan_w, chosen, None, x, E, mo), 10, 3, flush)
+        record(f"moe_combine, plain sum ({label})", us, nbytes=(rows + T) * width * 2, like=f"moe_combine, weighted ({label})")
+        us = 1e3 * _timed(lambda: K.moe_combine(y, plan_w, chosen, wts, x, E, mo), 10, 3, flush)
+        record(f"moe_combine, weighted ({label})", us, nbytes=(rows + T) * width * 2)
+    return out
+
+
 def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_source) -> dict:
     import torch
 
@@ -366,11 +543,15 @@ def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_
     llama = dict(llama, num_hidden_layers=len(lif["layers"]))
     flush = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")       # 256 MB: larger than L2
     t0 = time.time()
-    rows = [_model_runs(f"{family}-{shape}", lif, lif["vocab"], batch, context, steps, warmup, prefill_tokens, flush),
-            _model_runs(f"{llama_name} cut to {len(lif['layers'])} layers", llama, llama["vocab_size"], batch, context, steps, warmup,
-                        prefill_tokens, flush)]
-    alone = {"lifusun": _kernels_alone_lifusun, "rodapel": _kernels_alone_rodapel}[family](
-        lif, llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
+    rows = [_model_runs(f"{family}-{shape}", lif, lif["vocab"], batch, context, steps, warmup, prefill_tokens, flush)]
+    beside = None
+    if family == "fomerax":          # the closest family stands beside it too: latent and windowed attention, routed experts
+        _, beside = SHAPES[f"rodapel-{shape}"]
+        rows.append(_model_runs(f"rodapel-{shape}", beside, beside["vocab"], batch, context, steps, warmup, prefill_tokens, flush))
+    rows.append(_model_runs(f"{llama_name} cut to {len(lif['layers'])} layers", llama, llama["vocab_size"], batch, context, steps, warmup,
+                            prefill_tokens, flush))
+    alone = {"lifusun": _kernels_alone_lifusun, "rodapel": _kernels_alone_rodapel, "fomerax": _kernels_alone_fomerax}[family](
+        lif, beside if family == "fomerax" else llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
     return {"family": family, "shape": shape, "dtype": "bf16", "data": "synthetic (random weights, random tokens)",
             "models": rows, "kernels_alone": alone, "copy_bandwidth_gbs": peaks["hbm_gbs"], "peaks": f"of {source}",
             "l2": "256 MB written between timed runs", "steps": steps, "warmup": warmup, "seconds": round(time.time() - t0, 1)}

@@ -98,6 +98,36 @@ RODAPEL_3B = rodapel_shape(3072, 8192, 24, 8, 128, 128256, blocks=2)
 RODAPEL_1B = rodapel_shape(2048, 8192, 32, 8, 64, 128256, blocks=2)
 RODAPEL_TOY = rodapel_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=256, kv_rank=128, rot_dim=32, experts=4, identity=1)
 
+
+def fomerax_shape(width, inner, heads, kv_heads, head_dim, vocab, blocks, window=1024, kv_rank=512, rot_dim=64, q_rank=1536,
+                  experts=8, top=2, side_dim=256) -> dict:
+    """A Fomerax config.json of `blocks` groups of four layers (windowed latent attention with a dense feed-forward, biased
+    attention with routed ones, latent attention with routed ones, biased attention with a dense one), every layer with a
+    token input of `side_dim` columns, at the layer sizes of a Llama of the same width: for runs with random weights beside
+    the Rodapel and the Llama of that size.  A routed layer holds `experts` experts of half the dense inner width."""
+    lat = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank, "q_rank": q_rank,
+           "scale": (head_dim + rot_dim) ** -0.5, "mask": {"size": window},
+           "rot": {"dims": rot_dim, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "softcap": 50.0,
+           "q_temp": {"coef": 0.1, "every": 8192}}
+    dense = {"kind": "dense", "ff": inner}
+    routed = {"kind": "moe", "expert": {"ff": inner // 2}, "router": {"experts": experts, "top": top}}
+    layers = []
+    for _ in range(blocks):
+        layers += [{"type": "latent_attention", "mixer": copy.deepcopy(lat), "mlp": dict(dense)},
+                   {"type": "attention", "mixer": copy.deepcopy(att), "mlp": copy.deepcopy(routed)},
+                   {"type": "latent_attention", "mixer": copy.deepcopy(lat), "mlp": copy.deepcopy(routed)},
+                   {"type": "attention", "mixer": copy.deepcopy(att), "mlp": dict(dense)}]
+    return {"architecture": "Fomerax", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "token_side": {"dim": side_dim},
+            "layers": layers}
+
+
+# Fomerax at the layer sizes of the Llama shapes above (8 layers each)
+FOMERAX_8B = fomerax_shape(4096, 14336, 32, 8, 128, 128256, blocks=2)
+FOMERAX_3B = fomerax_shape(3072, 8192, 24, 8, 128, 128256, blocks=2, q_rank=1024)
+FOMERAX_1B = fomerax_shape(2048, 8192, 32, 8, 64, 128256, blocks=2, q_rank=768, side_dim=128)
+FOMERAX_TOY = fomerax_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=96, kv_rank=128, rot_dim=32, q_rank=192, experts=4, side_dim=32)
+
 # name -> (label used in reports, config.json dict)
 SHAPES = {
     "8b": ("llama-3.1-8b-shape-random", LLAMA_3_1_8B),
@@ -114,6 +144,10 @@ SHAPES = {
     "rodapel-3b": ("rodapel-3b-layers-random", RODAPEL_3B),
     "rodapel-1b": ("rodapel-1b-layers-random", RODAPEL_1B),
     "rodapel-toy": ("rodapel-toy-layers-random", RODAPEL_TOY),
+    "fomerax-8b": ("fomerax-8b-layers-random", FOMERAX_8B),
+    "fomerax-3b": ("fomerax-3b-layers-random", FOMERAX_3B),
+    "fomerax-1b": ("fomerax-1b-layers-random", FOMERAX_1B),
+    "fomerax-toy": ("fomerax-toy-layers-random", FOMERAX_TOY),
 }
 
 
