@@ -107,10 +107,15 @@ moe_plan_kernel(const int* __restrict__ chosen, int pairs, int top, int experts,
                 const int r = at + __popc(ballot & ((1u << lane) - 1u));
                 source[r] = i / top;
                 place[i] = r;
-                if (row_weight) row_weight[r] = weights[i];     // the pair's weight beside its sorted row
             }
             at += __popc(ballot);
         }
+    }
+    if (!row_weight) return;                // the same for the whole block
+    __syncthreads();                        // the places above were written by this block
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {     // the pair's weight beside its sorted row
+        const int r = place[i];
+        if (r >= 0) row_weight[r] = weights[i];
     }
 }
 

@@ -177,3 +177,34 @@ def test_greedy_generation_through_llm(dirs, device, name):
               device=device, kernels=kernels)
     outs = llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
     assert [o.token_ids for o in outs] == want
+
+
+@pytest.mark.gpu
+def test_command_line_serves_a_model_folder(dirs, tmp_path):
+    """The serving command line on a Fomerax folder (continuous batching under a small token budget, float32, greedy): every
+    request's ids equal the plain implementation's; and on a named shape of the family with random weights, sampled."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, seed, page = CONFIGS["B"]
+    prompts = list(cases.requests_for(cfg["vocab"], [3, 40, 17, 70, 5], seed + 60).values())
+    work, out = tmp_path / "w.jsonl", tmp_path / "res.json"
+    work.write_text("\n".join(json.dumps({"id": f"p{i}", "prompt_token_ids": p, "max_tokens": 5 + i}) for i, p in enumerate(prompts)))
+    proc = subprocess.run([sys.executable, "-m", "iitj_llm_coopt_b200.cli", "--model", dirs["B"], "--workload", str(work), "--out", str(out),
+                           "--num-pages", "64", "--page-size", str(page), "--max-num-seqs", "3", "--max-num-batched-tokens", "48",
+                           "--dtype", "float32", "--save-tokens"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    res = json.loads(out.read_text())
+    assert res["summary"]["completed"] == len(prompts) and res["summary"]["failed"] == 0
+    c, w = plain.read_model_dir(dirs["B"])
+    for i, (p, rec) in enumerate(zip(prompts, res["requests"])):
+        assert rec["token_ids"] == plain.greedy(c, w, p, 5 + i), i
+    proc = subprocess.run([sys.executable, "-m", "iitj_llm_coopt_b200.cli", "--shape", "fomerax-toy", "--random-seed", "5", "--workload",
+                           "synthetic:10:4-300:3-20", "--out", str(out), "--num-pages", "128", "--max-num-seqs", "4",
+                           "--max-num-batched-tokens", "64", "--save-tokens"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    res = json.loads(out.read_text())
+    assert res["summary"]["completed"] == 10 and res["summary"]["failed"] == 0
+    assert all(len(r["token_ids"]) == r["output_tokens"] == r["max_tokens"] for r in res["requests"])
