@@ -126,7 +126,7 @@ def fomerax_shape(width, inner, heads, kv_heads, head_dim, vocab, blocks, window
 FOMERAX_8B = fomerax_shape(4096, 14336, 32, 8, 128, 128256, blocks=2)
 FOMERAX_3B = fomerax_shape(3072, 8192, 24, 8, 128, 128256, blocks=2, q_rank=1024)
 FOMERAX_1B = fomerax_shape(2048, 8192, 32, 8, 64, 128256, blocks=2, q_rank=768, side_dim=128)
-FOMERAX_TOY = fomerax_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=96, kv_rank=128, rot_dim=32, q_rank=192, experts=4, side_dim=32)
+FOMERAX_TOY = fomerax_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=128, kv_rank=128, rot_dim=32, q_rank=192, experts=4, side_dim=32)
 
 # name -> (label used in reports, config.json dict)
 SHAPES = {
