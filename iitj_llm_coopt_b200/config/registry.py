@@ -54,4 +54,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import fomerax, lifusun, llama, rodapel  # noqa: F401  (they register themselves)
+        from ..models import fomerax, lifusun, llama, mamusun, rodapel  # noqa: F401  (they register themselves)

@@ -112,12 +112,25 @@ class TokenInputSpec:
 
 
 @dataclass(frozen=True)
+class StreamMixSpec:
+    """How a layer's result joins what earlier layers handed on: `inputs` weights over the embedding and the results of the
+    layers so far (this one's last); `total` is the most inputs any layer of the model mixes (the history's size)."""
+    kind: str                    # key in parts.STREAM_MIXES
+    width: int
+    inputs: int
+    total: int
+    options: tuple = ()
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: `arrangement` names how the parts are wired (parts.ARRANGEMENTS); `parts` holds one spec record
     for each part name the arrangement declares (its PARTS), as (name, spec) pairs.  `LayerSpec.of("prenorm",
-    mixer_norm=..., mixer=..., feed_forward_norm=..., feed_forward=...)` builds one from keywords."""
+    mixer_norm=..., mixer=..., feed_forward_norm=..., feed_forward=...)` builds one from keywords.  `options` are
+    constants of the arrangement itself ((name, value) pairs; the built arrangement finds them in `self.options`)."""
     arrangement: str
     parts: tuple = ()            # of (part name, spec record)
+    options: tuple = ()
 
     @classmethod
     def of(cls, arrangement: str, **parts) -> "LayerSpec":

@@ -12,7 +12,8 @@
 //                      optionally times sigmoid(gate) (one gate number per head, or one per output number).  The score of
 //                      query position p and key position j is  s = scale * temp(p) * q . k,  then  s = cap * tanh(s / cap)
 //                      (cap > 0),  then  s -= slope[head] * (p - j)  (slopes given), with the query temperature
-//                      temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)  (every > 0).  One warp per (token, head); keys are
+//                      temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)  (every > 0).  With `sinks` every row's denominator
+//                      also holds exp(sink[head]), a term without key or value that is neither scaled nor masked.  One warp per (token, head); keys are
 //                      walked in tiles of 32 that start at multiples of 32 of the key position, so a row's sums run in an
 //                      order that depends on its own position alone.
 #include "common.cuh"
@@ -145,7 +146,7 @@ attention_flat_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       const int* __restrict__ positions, const float* __restrict__ gate, int gate_cols, T* __restrict__ out,
                       int out_stride, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int shared_value,
                       int page_size, int window, float scale, float softcap, const float* __restrict__ slopes, float temp_coef,
-                      int temp_every, int vec) {
+                      int temp_every, const float* __restrict__ sinks, int vec) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float q_smem[];
@@ -208,6 +209,7 @@ attention_flat_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
         m = m_new;
     }
     T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
+    if (sinks) l += expf(sinks[h] - m);      // a term without a key or a value, once in the row's denominator
     float inv = 1.0f / l;
     if (gate && gate_cols == 1) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * heads + h]));
     const float* grow = gate && gate_cols > 1 ? gate + ((size_t)t * heads + h) * value_dim : nullptr;
@@ -255,7 +257,7 @@ LLM_API int llm_attention_flat(const void* q, int q_stride, const void* cache, l
                                int table_width, const int* token_request, const int* positions, const float* gate, int gate_cols,
                                void* out, int out_stride, int dtype, int tokens, int heads, int kv_heads, int key_dim, int value_dim,
                                int shared_value, int page_size, int window, float scale, float softcap, const float* slopes,
-                               float temp_coef, int temp_every, cudaStream_t stream) {
+                               float temp_coef, int temp_every, const float* sinks, cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (kv_heads <= 0 || heads % kv_heads) LLM_FAIL(-1, "attention_flat: heads %d is not a multiple of kv_heads %d", heads, kv_heads);
     if (value_dim <= 0 || value_dim > 512 || key_dim <= 0 || key_dim > 2048)
@@ -275,7 +277,7 @@ LLM_API int llm_attention_flat(const void* q, int q_stride, const void* cache, l
         llm_launch(attention_flat_kernel<T, OWN>, (unsigned)blocks, kWarps * 32, smem, stream, (const T*)q, q_stride,       \
                    (const T*)cache, page_stride, block_table, table_width, token_request, positions, gate, gate_cols, (T*)out,     \
                    out_stride, tokens, heads, kv_heads, key_dim, value_dim, shared_value, page_size, window, scale, softcap,    \
-                   slopes, temp_coef, temp_every, vec)
+                   slopes, temp_coef, temp_every, sinks, vec)
         if (value_dim <= 64) LLM_FLAT_CASE(2);
         else if (value_dim <= 128) LLM_FLAT_CASE(4);
         else if (value_dim <= 256) LLM_FLAT_CASE(8);

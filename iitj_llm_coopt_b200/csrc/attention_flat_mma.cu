@@ -33,6 +33,7 @@ struct FlatMmaArgs {
     const int* tiles; int n_tiles;            // (first token row, tokens, position of the first, request)
     const float* gate; int gate_cols;         // one gate number per head (1) or per output number (value_dim)
     const float* slopes;                      // per head: slope * (query position - key position) is taken off the score
+    const float* sinks;                       // per head: exp(sink) joins every row's denominator once, without a value (null: none)
     float softcap, temp_coef; int temp_every; // score squashing and query temperature (0: none), as in attention_flat.cu
     __nv_bfloat16* out; int out_stride;
     float* part_o; float* part_ml;            // [token, head, split, value_dim] and [token, head, split, 2] when splits > 1
@@ -257,6 +258,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         const int r = warp * 16 + gq + e * 8;
         const int t = row0 + r / hpb, head = kvh * group + hb * hpb + r % hpb;
         if (a.splits == 1) {
+            if (a.sinks) l[e] += expf(a.sinks[head] - m[e]);
             float inv = 1.0f / l[e];
             if (a.gate && a.gate_cols == 1) inv *= 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.heads + head]));
             const float* grow = a.gate && a.gate_cols > 1 ? a.gate + ((size_t)t * a.heads + head) * a.value_dim + slice0 : nullptr;
@@ -290,7 +292,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
 // out[t, head] = sum_s O_s e^(m_s - m) / sum_s l_s e^(m_s - m), times the gate; one block per (token, head).
 __global__ void __launch_bounds__(128)
 flat_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ gate, int gate_cols,
-                  __nv_bfloat16* __restrict__ out, int out_stride, int heads, int value_dim, int splits) {
+                  const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int out_stride, int heads, int value_dim, int splits) {
     pdl_trigger();
     pdl_wait();
     const size_t item = blockIdx.x;                       // token * heads + head
@@ -299,10 +301,11 @@ flat_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
     float l = 0.f;
     for (int s = 0; s < splits; ++s) l += ml[2 * s + 1] * (ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m));
+    const size_t t = item / heads, h = item % heads;
+    if (sinks) l += expf(sinks[h] - m);                   // once for the row, whatever the count of splits
     float inv = 1.0f / l;
     if (gate && gate_cols == 1) inv *= 1.0f / (1.0f + expf(-gate[item]));
     const float* grow = gate && gate_cols > 1 ? gate + item * value_dim : nullptr;
-    const size_t t = item / heads, h = item % heads;
     for (int d = threadIdx.x; d < value_dim; d += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < splits; ++s)
@@ -342,7 +345,7 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
                                    int table_width, const int* tiles, int n_tiles, const float* gate, int gate_cols, void* out,
                                    int out_stride, int tokens, int heads, int kv_heads, int key_dim, int value_dim, int shared_value,
                                    int page_size, int window, float scale, float softcap, const float* slopes, float temp_coef,
-                                   int temp_every, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                   int temp_every, int splits, float* part_o, float* part_ml, const float* sinks, cudaStream_t stream) {
     if (n_tiles == 0) return 0;
     if (!llm_attention_flat_mma_supported(heads, kv_heads, key_dim, value_dim, shared_value, page_stride))
         LLM_FAIL(-1, "attention_flat_mma: sizes not taken (key_dim %d, value_dim %d)", key_dim, value_dim);
@@ -354,7 +357,7 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
     FlatMmaArgs a;
     a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride; a.cache = (const __nv_bfloat16*)cache; a.page_stride = page_stride;
     a.block_table = block_table; a.table_width = table_width; a.tiles = tiles; a.n_tiles = n_tiles; a.gate = gate;
-    a.gate_cols = gate_cols; a.slopes = slopes; a.softcap = softcap; a.temp_coef = temp_coef; a.temp_every = temp_every;
+    a.gate_cols = gate_cols; a.slopes = slopes; a.sinks = sinks; a.softcap = softcap; a.temp_coef = temp_coef; a.temp_every = temp_every;
     a.out = (__nv_bfloat16*)out; a.out_stride = out_stride; a.part_o = part_o; a.part_ml = part_ml;
     a.heads = heads; a.kv_heads = kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.shared_value = shared_value;
     a.page_size = page_size; a.window = window; a.splits = splits; a.scale = scale;
@@ -380,7 +383,7 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
     LLM_CHECK_LAUNCH("attention_flat_mma");
     if (splits > 1) {
         llm_launch(flat_merge_kernel, (unsigned)(tokens * heads), 128, 0, stream, (const float*)part_o, (const float*)part_ml, gate,
-                   gate_cols, (__nv_bfloat16*)out, out_stride, heads, value_dim, splits);
+                   gate_cols, sinks, (__nv_bfloat16*)out, out_stride, heads, value_dim, splits);
         LLM_CHECK_LAUNCH("attention_flat_merge");
     }
     return 0;

@@ -1,0 +1,291 @@
+// A gated linear recurrence per channel (Griffin's recurrent unit with real gates), with its short causal convolution:
+//
+//   z_t = zx_t + bias_x                               (zx: the input branch's projection, columns [x_col, x_col + width) of `proj`)
+//   u_t = conv_bias + sum_j taps[:, j] z_(t - n + 1 + j)        n taps, the last is the current token's; zeros before a request's
+//                                                     first token; a request's last n - 1 rows of z are part of its state
+//   r_t = sigmoid(Ra u_t + ra_bias),  i_t = sigmoid(Ri u_t + ri_bias)     Ra, Ri block-diagonal: `blocks` square matrices [out, in]
+//   a_t = exp(-c r_t softplus(lam)),  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t       S float32, zero for a new request
+//   out_t = S_t * gelu_tanh(zy_t + bias_y)            (zy: the gate branch's projection, columns [y_col, y_col + width))
+//
+// Everything after the projections is float32; the weights of the gates are read as stored (the engine's type) and widened.
+// State per request: [taps, width] float32, row 0 is S, rows 1 .. taps - 1 the last rows of z, oldest first.
+//
+// llm_lru_conv:   u (float32 [tokens, width]) from proj and the state's rows of z.
+// llm_lru_gates:  a and b = sqrt(1 - a^2) i u (float32 [tokens, width]) from u; FMA tiles with a fixed order along k.
+// llm_lru_scan:   the recurrence, out, and the new state.  Short portions: one thread per (request, channel) walks the tokens.
+//                 Long portions are cut into segments of kSegment tokens: every segment's (product of a, end value from zero)
+//                 first, then the segments' starting values one after the other, then every segment again from its start.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kSegment = 64;
+
+__device__ __forceinline__ float gelu_tanh_lru(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+lru_conv_kernel(const T* __restrict__ proj, int ld, int x_col, const float* __restrict__ bias_x, const float* __restrict__ taps_w,
+                const float* __restrict__ conv_bias, int taps, const float* __restrict__ state, const int* __restrict__ state_slots,
+                const int* __restrict__ token_request, const int* __restrict__ cu_seqlens, float* __restrict__ u, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = token_request[t], start = cu_seqlens[b];
+    const float* st = state + (size_t)state_slots[b] * taps * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = conv_bias ? conv_bias[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = t - (taps - 1) + j;
+            // rows before the portion's first token come from the state: row 1 + (taps - 1) + (src - start)
+            const float z = src >= start ? to_f32(proj[(size_t)src * ld + x_col + c]) + (bias_x ? bias_x[c] : 0.f)
+                                         : st[(size_t)(taps + src - start) * width + c];
+            acc = fmaf(taps_w[(size_t)c * taps + j], z, acc);
+        }
+        u[(size_t)t * width + c] = acc;
+    }
+}
+
+constexpr int GT = 32, GN = 64, GK = 32;       // tokens x outputs of a block's tile, and the k chunk
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+lru_gates_kernel(const float* __restrict__ u, const T* __restrict__ ra, const T* __restrict__ ri, const float* __restrict__ ra_bias,
+                 const float* __restrict__ ri_bias, const float* __restrict__ lam, float decay_scale, float* __restrict__ a_out,
+                 float* __restrict__ b_out, int tokens, int width, int blocks) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float us[GT][GK + 1];
+    __shared__ float was[GN][GK + 1];
+    __shared__ float wis[GN][GK + 1];
+    const int bs = width / blocks;
+    const int col_tiles = (bs + GN - 1) / GN;
+    const int blk = blockIdx.y / col_tiles, n0 = (blockIdx.y % col_tiles) * GN;
+    const int t0 = blockIdx.x * GT;
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;      // outputs tx and tx + 32; tokens ty, ty + 8, ty + 16, ty + 24
+    float accr[4][2], acci[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { accr[i][0] = accr[i][1] = acci[i][0] = acci[i][1] = 0.f; }
+    const T* wa = ra + (size_t)blk * bs * bs;
+    const T* wi = ri + (size_t)blk * bs * bs;
+    for (int k0 = 0; k0 < bs; k0 += GK) {
+        for (int i = threadIdx.x; i < GT * GK; i += 256) {
+            const int r = i / GK, k = i % GK;
+            us[r][k] = (t0 + r < tokens && k0 + k < bs) ? u[(size_t)(t0 + r) * width + blk * bs + k0 + k] : 0.f;
+        }
+        for (int i = threadIdx.x; i < GN * GK; i += 256) {
+            const int r = i / GK, k = i % GK;
+            const bool ok = n0 + r < bs && k0 + k < bs;
+            was[r][k] = ok ? to_f32(wa[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+            wis[r][k] = ok ? to_f32(wi[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < GK; ++k) {
+            const float a0 = was[tx][k], a1 = was[tx + 32][k], i0 = wis[tx][k], i1 = wis[tx + 32][k];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float uv = us[ty + 8 * i][k];
+                accr[i][0] = fmaf(uv, a0, accr[i][0]);
+                accr[i][1] = fmaf(uv, a1, accr[i][1]);
+                acci[i][0] = fmaf(uv, i0, acci[i][0]);
+                acci[i][1] = fmaf(uv, i1, acci[i][1]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int t = t0 + ty + 8 * i, n = n0 + tx + 32 * j;
+            if (t >= tokens || n >= bs) continue;
+            const int c = blk * bs + n;
+            const float r = 1.0f / (1.0f + expf(-(accr[i][j] + ra_bias[c])));
+            const float g = 1.0f / (1.0f + expf(-(acci[i][j] + ri_bias[c])));
+            const float l = lam[c];
+            const float sp = l > 20.f ? l : log1pf(expf(l));
+            const float a = expf(-decay_scale * r * sp);
+            a_out[(size_t)t * width + c] = a;
+            b_out[(size_t)t * width + c] = sqrtf(fmaxf(1.0f - a * a, 0.f)) * g * u[(size_t)t * width + c];
+        }
+}
+
+// The new rows of z of a request's state, for channel c: the last taps - 1 of (old rows, this portion's rows).
+template <typename T>
+__device__ __forceinline__ void lru_shift_state(float* st, const T* __restrict__ proj, int ld, int x_col, const float* __restrict__ bias_x,
+                                                int taps, int start, int end, int width, int c) {
+    const int keep = taps - 1, n = end - start;
+    float held[8];
+    for (int j = 0; j < keep; ++j) {
+        const int src = end - keep + j;                 // token row; before `start`: the state's row keep + (src - start)
+        held[j] = src >= start ? to_f32(proj[(size_t)src * ld + x_col + c]) + (bias_x ? bias_x[c] : 0.f)
+                               : st[(size_t)(1 + keep + src - start) * width + c];
+    }
+    (void)n;
+    for (int j = 0; j < keep; ++j) st[(size_t)(1 + j) * width + c] = held[j];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+lru_scan_walk_kernel(const float* __restrict__ a, const float* __restrict__ b, const T* __restrict__ proj, int ld, int y_col, int x_col,
+                     const float* __restrict__ bias_y, const float* __restrict__ bias_x, int taps, float* __restrict__ state,
+                     const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens, T* __restrict__ out, int width, int write) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= width) return;
+    const int start = cu_seqlens[r], end = cu_seqlens[r + 1];
+    float* st = state + (size_t)state_slots[r] * taps * width;
+    float S = st[c];
+    const float by = bias_y ? bias_y[c] : 0.f;
+    for (int t = start; t < end; ++t) {
+        S = fmaf(a[(size_t)t * width + c], S, b[(size_t)t * width + c]);
+        out[(size_t)t * width + c] = from_f32<T>(S * gelu_tanh_lru(to_f32(proj[(size_t)t * ld + y_col + c]) + by));
+    }
+    if (write && end > start) {
+        st[c] = S;
+        lru_shift_state(st, proj, ld, x_col, bias_x, taps, start, end, width, c);
+    }
+}
+
+// pass 1: every segment's product of a and its end value from zero
+__global__ void __launch_bounds__(128)
+lru_segment_sums_kernel(const float* __restrict__ a, const float* __restrict__ b, const int* __restrict__ cu_seqlens,
+                        float* __restrict__ seg_a, float* __restrict__ seg_b, int width, int segments) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y / segments, s = blockIdx.y % segments;
+    if (c >= width) return;
+    const int start = cu_seqlens[r] + s * kSegment, end = min(cu_seqlens[r + 1], start + kSegment);
+    float A = 1.f, B = 0.f;
+    for (int t = start; t < end; ++t) {
+        const float at = a[(size_t)t * width + c];
+        A *= at;
+        B = fmaf(at, B, b[(size_t)t * width + c]);
+    }
+    seg_a[(size_t)blockIdx.y * width + c] = A;
+    seg_b[(size_t)blockIdx.y * width + c] = B;
+}
+
+// pass 2: the segments' starting values, one after the other (left in seg_b), the new state
+template <typename T>
+__global__ void __launch_bounds__(128)
+lru_segment_starts_kernel(const float* __restrict__ seg_a, float* __restrict__ seg_b, const T* __restrict__ proj, int ld, int x_col,
+                          const float* __restrict__ bias_x, int taps, float* __restrict__ state, const int* __restrict__ state_slots,
+                          const int* __restrict__ cu_seqlens, int width, int segments, int write) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= width) return;
+    const int start = cu_seqlens[r], end = cu_seqlens[r + 1];
+    float* st = state + (size_t)state_slots[r] * taps * width;
+    float S = st[c];
+    const int used = (end - start + kSegment - 1) / kSegment;
+    for (int s = 0; s < used; ++s) {
+        const size_t at = ((size_t)r * segments + s) * width + c;
+        const float next = fmaf(seg_a[at], S, seg_b[at]);
+        seg_b[at] = S;
+        S = next;
+    }
+    if (write && end > start) {
+        st[c] = S;
+        lru_shift_state(st, proj, ld, x_col, bias_x, taps, start, end, width, c);
+    }
+}
+
+// pass 3: every segment again, from its starting value
+template <typename T>
+__global__ void __launch_bounds__(128)
+lru_segment_apply_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ seg_start,
+                         const T* __restrict__ proj, int ld, int y_col, const float* __restrict__ bias_y,
+                         const int* __restrict__ cu_seqlens, T* __restrict__ out, int width, int segments) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y / segments, s = blockIdx.y % segments;
+    if (c >= width) return;
+    const int start = cu_seqlens[r] + s * kSegment, end = min(cu_seqlens[r + 1], start + kSegment);
+    if (start >= end) return;
+    float S = seg_start[(size_t)blockIdx.y * width + c];
+    const float by = bias_y ? bias_y[c] : 0.f;
+    for (int t = start; t < end; ++t) {
+        S = fmaf(a[(size_t)t * width + c], S, b[(size_t)t * width + c]);
+        out[(size_t)t * width + c] = from_f32<T>(S * gelu_tanh_lru(to_f32(proj[(size_t)t * ld + y_col + c]) + by));
+    }
+}
+
+}  // namespace
+
+LLM_API int llm_lru_segment() { return kSegment; }
+
+// proj [tokens, ld] of `dtype`; bias_x, conv_bias float32 [width] or null; taps_w float32 [width, taps]; state float32 [slots, taps, width];
+// u float32 [tokens, width].
+LLM_API int llm_lru_conv(const void* proj, int ld, int x_col, const float* bias_x, const float* taps_w, const float* conv_bias, int taps,
+                         const float* state, const int* state_slots, const int* token_request, const int* cu_seqlens, float* u,
+                         int dtype, int tokens, int width, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (taps < 1 || taps > 9) LLM_FAIL(-1, "lru_conv: %d taps (1 to 9)", taps);
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        llm_launch(lru_conv_kernel<T>, (unsigned)tokens, 256, 0, stream, (const T*)proj, ld, x_col, bias_x, taps_w, conv_bias, taps, state,
+                   state_slots, token_request, cu_seqlens, u, width);
+        LLM_CHECK_LAUNCH("lru_conv");
+        return 0;
+    });
+}
+
+// ra, ri [blocks, width / blocks, width / blocks] of `dtype` ([out, in] each); biases and lam float32 [width]; a_out, b_out float32.
+LLM_API int llm_lru_gates(const float* u, const void* ra, const void* ri, const float* ra_bias, const float* ri_bias, const float* lam,
+                          float decay_scale, float* a_out, float* b_out, int dtype, int tokens, int width, int blocks,
+                          cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (blocks < 1 || width % blocks) LLM_FAIL(-1, "lru_gates: width %d is not a multiple of %d blocks", width, blocks);
+    const int bs = width / blocks;
+    dim3 grid((unsigned)((tokens + GT - 1) / GT), (unsigned)(blocks * ((bs + GN - 1) / GN)));
+    if (grid.y > 65535) LLM_FAIL(-1, "lru_gates: too many column tiles");
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        llm_launch(lru_gates_kernel<T>, grid, 256, 0, stream, u, (const T*)ra, (const T*)ri, ra_bias, ri_bias, lam, decay_scale, a_out,
+                   b_out, tokens, width, blocks);
+        LLM_CHECK_LAUNCH("lru_gates");
+        return 0;
+    });
+}
+
+// longest: the most tokens a request brings (chooses the walk or the segments); scratch: float32 [2 * requests * segments * width]
+// with segments = ceil(longest / llm_lru_segment()), needed when longest > llm_lru_segment().
+LLM_API int llm_lru_scan(const float* a, const float* b, const void* proj, int ld, int y_col, int x_col, const float* bias_y,
+                         const float* bias_x, int taps, float* state, const int* state_slots, const int* cu_seqlens, void* out,
+                         int dtype, int requests, int width, int longest, int write, float* scratch, cudaStream_t stream) {
+    if (requests == 0 || longest == 0) return 0;
+    if (taps < 1 || taps > 9) LLM_FAIL(-1, "lru_scan: %d taps (1 to 9)", taps);
+    const unsigned cb = (unsigned)((width + 127) / 128);
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        if (longest <= kSegment) {
+            llm_launch(lru_scan_walk_kernel<T>, dim3(cb, (unsigned)requests), 128, 0, stream, a, b, (const T*)proj, ld, y_col, x_col, bias_y,
+                       bias_x, taps, state, state_slots, cu_seqlens, (T*)out, width, write);
+            LLM_CHECK_LAUNCH("lru_scan");
+            return 0;
+        }
+        if (!scratch) LLM_FAIL(-1, "lru_scan: segments need scratch");
+        const int segments = (longest + kSegment - 1) / kSegment;
+        if ((long long)requests * segments > 65535) LLM_FAIL(-1, "lru_scan: too many segments");
+        float* seg_a = scratch;
+        float* seg_b = scratch + (size_t)requests * segments * width;
+        llm_launch(lru_segment_sums_kernel, dim3(cb, (unsigned)(requests * segments)), 128, 0, stream, a, b, cu_seqlens, seg_a, seg_b, width,
+                   segments);
+        LLM_CHECK_LAUNCH("lru_segment_sums");
+        llm_launch(lru_segment_starts_kernel<T>, dim3(cb, (unsigned)requests), 128, 0, stream, (const float*)seg_a, seg_b, (const T*)proj, ld,
+                   x_col, bias_x, taps, state, state_slots, cu_seqlens, width, segments, write);
+        LLM_CHECK_LAUNCH("lru_segment_starts");
+        llm_launch(lru_segment_apply_kernel<T>, dim3(cb, (unsigned)(requests * segments)), 128, 0, stream, a, b, (const float*)seg_b,
+                   (const T*)proj, ld, y_col, bias_y, cu_seqlens, (T*)out, width, segments);
+        LLM_CHECK_LAUNCH("lru_segment_apply");
+        return 0;
+    });
+}
+
+LLM_TRACE_EXPORT(lru)

@@ -3,7 +3,8 @@
 //
 // llm_route_topk:   s = softmax(z) over all router outputs, or sigmoid(z) of each (float32); the `top` largest of
 //                   s + correction (null: of s) are chosen (ties: the lower index), in descending order; the weights are the
-//                   chosen s, not renormalised.  One warp per token.
+//                   chosen s, not renormalised.  A third form compares z + bias itself (the bias where `correction` would be) and
+//                   takes the softmax over the chosen outputs alone as weights.  One warp per token.
 // llm_moe_plan:     the (token, choice) pairs sorted by expert, stable in the pair's index: source[r] = token of sorted row r,
 //                   place[token * top + j] = sorted row of that pair (-1 for a choice >= experts: an expert without tensors),
 //                   and the list of row tiles (expert, first row, rows) that llm_gemm_grouped walks, with its count in front.
@@ -26,7 +27,10 @@ route_topk_kernel(const float* __restrict__ z, const float* __restrict__ correct
     float* s = route_smem + (size_t)warp * 2 * outputs;      // scores, then choice scores
     float* c = s + outputs;
     const float* row = z + (size_t)t * outputs;
-    if (sigmoid) {
+    if (sigmoid == 2) {
+        // the outputs themselves (plus a bias, where one is given) are compared; the weights are made after the choice
+        for (int i = lane; i < outputs; i += 32) { s[i] = row[i] + (correction ? correction[i] : 0.f); c[i] = s[i]; }
+    } else if (sigmoid) {
         for (int i = lane; i < outputs; i += 32) { s[i] = 1.0f / (1.0f + expf(-row[i])); c[i] = s[i] + (correction ? correction[i] : 0.f); }
     } else {
         float m = -INFINITY;
@@ -56,6 +60,15 @@ route_topk_kernel(const float* __restrict__ z, const float* __restrict__ correct
             c[at] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (sigmoid == 2 && lane == 0) {
+        // softmax over the chosen outputs alone; the first choice is the largest
+        float* w = weights + (size_t)t * top;
+        const float m = w[0];
+        float sum = 0.f;
+        for (int j = 0; j < top; ++j) { w[j] = expf(w[j] - m); sum += w[j]; }
+        const float inv = 1.0f / sum;
+        for (int j = 0; j < top; ++j) w[j] *= inv;
     }
 }
 
@@ -181,6 +194,7 @@ LLM_API int llm_route_topk(const float* z, const float* correction, int* chosen,
                            int sigmoid, cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (top < 1 || top > outputs) LLM_FAIL(-1, "route_topk: %d of %d outputs", top, outputs);
+    if (sigmoid < 0 || sigmoid > 2) LLM_FAIL(-1, "route_topk: form %d is not known (0 softmax, 1 sigmoid, 2 softmax over the chosen)", sigmoid);
     const size_t smem = (size_t)4 * 2 * outputs * sizeof(float);
     if (smem > 48 * 1024) LLM_FAIL(-1, "route_topk: %d router outputs are more than 1536", outputs);
     llm_launch(route_topk_kernel, (unsigned)((tokens + 3) / 4), 128, smem, stream, z, correction, chosen, weights, tokens, outputs, top,

@@ -114,13 +114,27 @@ _SIGNATURES = {
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "llm_attention_flat": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                           _c_float, _c_void_p, _c_float, _c_int, _c_void_p],
+                           _c_float, _c_void_p, _c_float, _c_int, _c_void_p, _c_void_p],
     "llm_attention_flat_mma_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_longlong],
     "llm_attention_flat_mma_heads_per_block": [_c_int, _c_int],
     "llm_attention_flat_mma_smem": [_c_int, _c_int, _c_int],
     "llm_attention_flat_mma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
                                _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                               _c_float, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+                               _c_float, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "llm_qk_prepare": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_float, _c_void_p],
+    "llm_post_norm": [_c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                      _c_void_p, _c_int, ctypes.c_longlong, _c_int, _c_int, _c_void_p],
+    "llm_branch_mean": [_c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_int, _c_int, _c_void_p],
+    "llm_poly_norm": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_lru_segment": [],
+    "llm_lru_conv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                     _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_lru_gates": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int,
+                      _c_int, _c_int, _c_int, _c_void_p],
+    "llm_lru_scan": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                     _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "llm_gemm_grouped_tile_rows": [],
     "llm_gemm_grouped": [_c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p,
                          ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -891,10 +905,11 @@ class Kernels:
                    _ptr(out_gate), self._stream())
         return out
 
-    def route_topk(self, scores, correction, chosen, weights, sigmoid: bool = False):
+    def route_topk(self, scores, correction, chosen, weights, sigmoid: bool = False, chosen_softmax: bool = False):
         """Router outputs [T, R] float32 -> chosen [T, top] int32 (the largest s + correction, descending; correction None: of
         s) and weights [T, top] float32 (their s), where s is the softmax over the outputs, or with `sigmoid` each output's
-        sigmoid; csrc/moe_route.cu."""
+        sigmoid.  `chosen_softmax`: the outputs themselves are compared, plus `correction` as a bias that belongs to them, and
+        the weights are the softmax over the chosen outputs alone; csrc/moe_route.cu."""
         _check(scores, "route_topk.scores", torch.float32, 2)
         if correction is not None:
             _check(correction, "route_topk.correction", torch.float32, 1)
@@ -904,7 +919,7 @@ class Kernels:
         _need((correction is None or correction.shape[0] == outputs) and chosen.shape[0] == tokens and
               tuple(weights.shape) == tuple(chosen.shape), "route_topk: shapes do not fit")
         self._call("llm_route_topk", _ptr(scores), _ptr(correction), _ptr(chosen), _ptr(weights), tokens, outputs, chosen.shape[1],
-                   1 if sigmoid else 0, self._stream())
+                   2 if chosen_softmax else 1 if sigmoid else 0, self._stream())
 
     def moe_tile_bound(self, rows: int, experts: int) -> int:
         """The most row tiles `moe_plan` can make of `rows` (token, choice) pairs over `experts` experts."""
@@ -1069,14 +1084,18 @@ class Kernels:
 
     def attention_flat(self, q, cache_layer, meta, out, heads, kv_heads, key_dim, value_dim, shared_value: bool = False,
                        window: int = 0, scale: float = 1.0, gate=None, plan=None, softcap: float = 0.0, slopes=None,
-                       q_temp=None):
+                       q_temp=None, sinks=None):
         """Attention of every token's query heads (the leading heads * key_dim numbers of q's rows) over the flat-page
         cache of its request: keys of key_dim, values of value_dim (`shared_value`: the leading value_dim numbers of the key
         rows), a sliding window (0: all earlier keys), optionally the output times sigmoid(gate) (gate [T, heads]: a number
         per head; [T, heads * value_dim]: per output number).  Score options: `softcap` c > 0 squashes the scaled score to
         c tanh(s / c); `slopes` [heads] float32 takes slope * (query position - key position) off; `q_temp` = (coef, every)
-        multiplies the query at position p by 1 + coef ln(floor((p + 1) / every) + 1)."""
+        multiplies the query at position p by 1 + coef ln(floor((p + 1) / every) + 1); `sinks` [heads] float32 puts exp(sink) of
+        the head into every row's denominator, a term without key or value that is neither scaled nor masked."""
         _check(q, "attention_flat.q", tuple(DTYPE_CODE), 2)
+        if sinks is not None:
+            _check(sinks, "attention_flat.sinks", torch.float32, 1)
+            _need(sinks.shape[0] == heads, "attention_flat.sinks: one per head")
         _check(cache_layer, "attention_flat.cache", q.dtype, 2)
         _check(out, "attention_flat.out", q.dtype, 2)
         tokens = q.shape[0]
@@ -1110,14 +1129,155 @@ class Kernels:
             self._call("llm_attention_flat_mma", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
                        meta.block_table.shape[1], _ptr(tiles), tiles.shape[0] // 4, _ptr(gate), gate_cols, _ptr(out), out.shape[1],
                        tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size, int(window), float(scale),
-                       float(softcap), _ptr(slopes), coef, every, splits, _ptr(part_o), _ptr(part_ml), self._stream())
+                       float(softcap), _ptr(slopes), coef, every, splits, _ptr(part_o), _ptr(part_ml), _ptr(sinks), self._stream())
             if splits > 1:
                 self.launches += 1      # the merge kernel
             return out
         self._call("llm_attention_flat", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
                    meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(gate), gate_cols, _ptr(out),
                    out.shape[1], DTYPE_CODE[q.dtype], tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size,
-                   int(window), float(scale), float(softcap), _ptr(slopes), coef, every, self._stream())
+                   int(window), float(scale), float(softcap), _ptr(slopes), coef, every, _ptr(sinks), self._stream())
+        return out
+
+    def qk_prepare(self, proj, heads, kv_heads, dim, vdim, eps, cache_layer=None, slots=None, bias=None, norm: str = "none",
+                   q_gain=None, k_gain=None, norm_first: bool = True, tables=None, rotary_dim: int = 0, interleaved: bool = False,
+                   own_kv: bool = True, value_from_key: bool = False):
+        """Between a grouped attention's fused projection and its attention kernel (csrc/qk_prepare.cu), per token:
+        proj [T, heads * dim (+ kv_heads * dim (+ kv_heads * vdim))] gets `bias` (float32, one per column) added; the values
+        are the keys at that point (`value_from_key`) or the v columns; queries and keys are normed (`norm` "head": every head
+        by its root mean square with gains [dim] shared by the heads, or none; "row": all of q, and all of k, at once with
+        gains of that size) and their leading `rotary_dim` numbers rotated by `tables` = (cos, sin) float32 [T, rotary_dim / 2],
+        the norm first or the rotation first; queries go back in place, keys and values into the flat-page cache at `slots`
+        (None: no store).  `own_kv` False: proj holds queries alone."""
+        _check(proj, "qk_prepare.proj", tuple(DTYPE_CODE), 2)
+        tokens = proj.shape[0]
+        q_cols, k_cols = heads * dim, kv_heads * dim if own_kv else 0
+        v_cols = kv_heads * vdim if own_kv and not value_from_key else 0
+        _need(proj.shape[1] == q_cols + k_cols + v_cols, "qk_prepare.proj: wrong width")
+        _need(norm in ("none", "head", "row"), "qk_prepare: norm is none, head or row")
+        if bias is not None:
+            _check(bias, "qk_prepare.bias", torch.float32, 1)
+            _need(bias.shape[0] >= q_cols + k_cols, "qk_prepare.bias: one per query and key column")
+            _need(v_cols == 0 or bias.shape[0] == proj.shape[1], "qk_prepare.bias: one per column")
+        for name, g, n in (("q_gain", q_gain, dim if norm == "head" else q_cols), ("k_gain", k_gain, dim if norm == "head" else k_cols)):
+            if g is not None:
+                _check(g, "qk_prepare." + name, torch.float32, 1)
+                _need(norm != "none" and g.shape[0] == n, f"qk_prepare.{name}: {n} gains")
+        cos = sin = None
+        if rotary_dim:
+            cos, sin = tables
+            _check(cos, "qk_prepare.cos", torch.float32, 2)
+            _check(sin, "qk_prepare.sin", torch.float32, 2)
+            _need(cos.shape == (tokens, rotary_dim // 2) and sin.shape == cos.shape, "qk_prepare: tables must be [tokens, rotary_dim / 2]")
+        page_size, stride = 1, 0
+        if slots is not None:
+            _need(own_kv, "qk_prepare: a layer without keys of its own stores nothing")
+            _check(slots, "qk_prepare.slots", torch.int32, 1)
+            _check(cache_layer, "qk_prepare.cache", proj.dtype, 2)
+            _need(slots.shape[0] == tokens, "qk_prepare.slots: one per token")
+            page_size, stride = self._flat_page_size(cache_layer, kv_heads, dim, vdim, False), cache_layer.shape[1]
+        self._call("llm_qk_prepare", _ptr(proj), proj.shape[1], _ptr(bias), _ptr(q_gain), _ptr(k_gain), _ptr(cos), _ptr(sin),
+                   _ptr(cache_layer) if slots is not None else None, _ptr(slots), stride, page_size, DTYPE_CODE[proj.dtype], tokens,
+                   heads, kv_heads, dim, vdim, {"none": 0, "head": 1, "row": 2}[norm], 1 if norm_first else 0, int(rotary_dim),
+                   1 if interleaved else 0, 1 if own_kv else 0, 1 if value_from_key else 0, float(eps), self._stream())
+        return proj
+
+    # ---- norms behind the sum, depth average, normed branches, normed polynomial activation ---------------------
+    def post_norm(self, x, branch, alpha: float, gain, eps: float, out, cast_out=None, history=None, mix=None):
+        """y = rmsnorm(alpha * x + branch) * gain with float32 statistics (csrc/post_norm.cu); x, out float32 [T, w] (may be the
+        same), gain float32 as it multiplies.  With `history` float32 [inputs, T, w] and `mix` float32 [inputs]: y becomes the
+        history's last entry and `out` receives sum_j mix[j] * history[j].  `cast_out`: what `out` got, in another type."""
+        _check(x, "post_norm.x", torch.float32, 2)
+        _check(out, "post_norm.out", torch.float32, 2)
+        _check(branch, "post_norm.branch", tuple(DTYPE_CODE), 2)
+        _check(gain, "post_norm.gain", torch.float32, 1)
+        tokens, width = x.shape
+        _need(tuple(branch.shape) == (tokens, width) and tuple(out.shape) == (tokens, width) and gain.shape[0] == width,
+              "post_norm: shapes differ")
+        if cast_out is not None:
+            _check(cast_out, "post_norm.cast_out", tuple(DTYPE_CODE), 2)
+            _need(cast_out.shape == x.shape, "post_norm.cast_out: shape differs")
+        inputs = 0
+        if history is not None:
+            _check(history, "post_norm.history", torch.float32, 3)
+            _check(mix, "post_norm.mix", torch.float32, 1)
+            inputs = mix.shape[0]
+            _need(history.shape[0] >= inputs >= 1 and tuple(history.shape[1:]) == (tokens, width), "post_norm.history: [inputs, T, w]")
+        self._call("llm_post_norm", _ptr(x), _ptr(branch), DTYPE_CODE[branch.dtype], float(alpha), _ptr(gain), float(eps), _ptr(out),
+                   _ptr(cast_out), DTYPE_CODE[cast_out.dtype] if cast_out is not None else 0, _ptr(history), _ptr(mix), inputs,
+                   tokens * width, tokens, width, self._stream())
+        return out
+
+    def branch_mean(self, branches, gains, scale: float, eps: float, out):
+        """out (float32) = scale * sum_b rmsnorm(branches[b]) * gains[b], one to four branches of the engine's type."""
+        _need(1 <= len(branches) <= 4 and len(gains) == len(branches), "branch_mean: one to four branches, a gain vector each")
+        _check(out, "branch_mean.out", torch.float32, 2)
+        for b, g in zip(branches, gains):
+            _check(b, "branch_mean.branch", branches[0].dtype, 2)
+            _check(g, "branch_mean.gain", torch.float32, 1)
+            _need(b.shape == out.shape and g.shape[0] == out.shape[1], "branch_mean: shapes differ")
+        _need(branches[0].dtype in DTYPE_CODE, "branch_mean: branches of one of the engine's types")
+        n = len(branches)
+        bp = (ctypes.c_void_p * n)(*[b.data_ptr() for b in branches])
+        gp = (ctypes.c_void_p * n)(*[g.data_ptr() for g in gains])
+        self._call("llm_branch_mean", ctypes.cast(bp, ctypes.c_void_p), ctypes.cast(gp, ctypes.c_void_p), n,
+                   DTYPE_CODE[branches[0].dtype], float(scale), float(eps), _ptr(out), out.shape[0], out.shape[1], self._stream())
+        return out
+
+    def poly_norm(self, z, coef, eps: float, act):
+        """act = a N(z) + b N(z^2) + c N(z^3) + e over every row of z, N dividing a row by its root mean square; coef float32 [4]."""
+        _check(z, "poly_norm.z", tuple(DTYPE_CODE), 2)
+        _check(act, "poly_norm.act", z.dtype, 2)
+        _check(coef, "poly_norm.coef", torch.float32, 1)
+        _need(act.shape == z.shape and coef.shape[0] == 4, "poly_norm: shapes do not fit")
+        self._call("llm_poly_norm", _ptr(z), _ptr(coef), float(eps), _ptr(act), DTYPE_CODE[z.dtype], z.shape[0], z.shape[1], self._stream())
+        return act
+
+    # ---- gated linear recurrence ------------------------------------------------------------------------------------
+    def lru(self, proj, y_col: int, x_col: int, width: int, bias_y, bias_x, taps_w, conv_bias, ra, ri, ra_bias, ri_bias, lam,
+            decay_scale: float, state, state_slots, token_request, cu_seqlens, out, longest: int, write: bool = True):
+        """A gated linear recurrence per channel with its short convolution (csrc/lru.cu): proj [T, ld] holds the gate branch's
+        projection at columns [y_col, y_col + width) and the input branch's at [x_col, ...); state float32 [slots, taps, width]
+        (row 0 the recurrence's state, then the last taps - 1 inputs of the convolution); out [T, width] of proj's type."""
+        _check(proj, "lru.proj", tuple(DTYPE_CODE), 2)
+        _check(out, "lru.out", proj.dtype, 2)
+        tokens = proj.shape[0]
+        _need(max(y_col, x_col) + width <= proj.shape[1] and tuple(out.shape) == (tokens, width), "lru: proj / out shapes do not fit")
+        _check(taps_w, "lru.taps", torch.float32, 2)
+        taps = taps_w.shape[1]
+        _need(taps_w.shape[0] == width, "lru.taps: one row per channel")
+        for name, t in (("bias_y", bias_y), ("bias_x", bias_x), ("conv_bias", conv_bias), ("ra_bias", ra_bias), ("ri_bias", ri_bias), ("lam", lam)):
+            if t is not None:
+                _check(t, "lru." + name, torch.float32, 1)
+                _need(t.shape[0] == width, f"lru.{name}: one per channel")
+        _need(ra_bias is not None and ri_bias is not None and lam is not None, "lru: gate biases and decay parameters are needed")
+        _check(ra, "lru.ra", proj.dtype, 3)
+        _check(ri, "lru.ri", proj.dtype, 3)
+        blocks = ra.shape[0]
+        _need(width % blocks == 0 and tuple(ra.shape) == (blocks, width // blocks, width // blocks) and ri.shape == ra.shape,
+              "lru: gate matrices are [blocks, width / blocks, width / blocks]")
+        _check(state, "lru.state", torch.float32, 3)
+        _need(tuple(state.shape[1:]) == (taps, width), "lru.state: [slots, taps, width]")
+        for name, t in (("state_slots", state_slots), ("token_request", token_request), ("cu_seqlens", cu_seqlens)):
+            _check(t, "lru." + name, torch.int32, 1)
+        requests = state_slots.shape[0]
+        _need(token_request.shape[0] == tokens and cu_seqlens.shape[0] == requests + 1, "lru: index arrays do not fit")
+        u = self._scratch("lru.u", tokens * width, proj.device)
+        a = self._scratch("lru.a", tokens * width, proj.device)
+        b = self._scratch("lru.b", tokens * width, proj.device)
+        code = DTYPE_CODE[proj.dtype]
+        self._call("llm_lru_conv", _ptr(proj), proj.shape[1], int(x_col), _ptr(bias_x), _ptr(taps_w), _ptr(conv_bias), taps, _ptr(state),
+                   _ptr(state_slots), _ptr(token_request), _ptr(cu_seqlens), _ptr(u), code, tokens, width, self._stream())
+        self._call("llm_lru_gates", _ptr(u), _ptr(ra), _ptr(ri), _ptr(ra_bias), _ptr(ri_bias), _ptr(lam), float(decay_scale), _ptr(a),
+                   _ptr(b), code, tokens, width, blocks, self._stream())
+        seg = self.lib.llm_lru_segment()
+        scratch = None
+        if longest > seg:
+            scratch = self._scratch("lru.segments", 2 * requests * -(-longest // seg) * width, proj.device)
+            self.launches += 2
+        self._call("llm_lru_scan", _ptr(a), _ptr(b), _ptr(proj), proj.shape[1], int(y_col), int(x_col), _ptr(bias_y), _ptr(bias_x), taps,
+                   _ptr(state), _ptr(state_slots), _ptr(cu_seqlens), _ptr(out), code, requests, width, int(longest), 1 if write else 0,
+                   _ptr(scratch), self._stream())
         return out
 
     def token_shift(self, x, mu, before, state_slots, token_request, cu_seqlens, out):

@@ -107,7 +107,9 @@ class DecoderModel:
         for layer in spec.layers:
             built = {name: build_part(family, part_spec, cls, kernels, dtype, device, name)
                      for name, family, part_spec, cls in layer_parts(layer)}
-            self.layers.append(_arrangement(layer)(**built))
+            block = _arrangement(layer)(**built)
+            block.options = dict(getattr(layer, "options", ()))
+            self.layers.append(block)
         self.final_norm = build_part("norm", spec.final_norm, _lookup("norm", spec.final_norm, "norm"), kernels, dtype, device,
                                      "final_norm")
         head = spec.head_spec()

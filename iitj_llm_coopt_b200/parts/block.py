@@ -23,6 +23,7 @@ from .base import delta_for
 
 class Arrangement:
     PARTS: dict = {}             # part name -> family
+    options: dict = {}           # the layer spec's constants of the arrangement itself (set by the model builder)
 
     def __init__(self, **parts):
         missing = [n for n in self.PARTS if n not in parts]
@@ -174,3 +175,72 @@ class SandwichSideBlock(SandwichBlock):
 
 class SandwichMixerSideBlock(SandwichMixerBlock):
     PARTS = dict(SandwichMixerBlock.PARTS, token_input="token_input")
+
+
+class PostNormDepthBlock(Arrangement):
+    """Norms behind the sums, a scaled residual, and a mix over depth at the layer's end:
+
+        x1 = mixer_norm(alpha * x + mixer(x))
+        X  = feed_forward_norm(alpha * x1 + feed_forward(x1))
+        what the next layer reads = stream_mix over the embedding's output and every layer's X so far
+
+    `alpha` is the arrangement's option.  The sub-layers read the stream as the engine's type (a rounded copy that the norm
+    kernels write on the way); the stream, the sums and the norms are float32.  The last norm of the layer, the store of X in
+    the step's history and the weighted sum over it are one kernel (`Kernels.post_norm`)."""
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm",
+             "stream_mix": "stream_mix"}
+    CAST = BranchNormBlock.CAST
+
+    def _enter(self, ctx, residual, delta):
+        """(the float32 stream, its copy of the engine's type)"""
+        if delta is not None:
+            residual.add_(delta_for(None, delta))
+            ctx.shared.pop(self.CAST, None)
+        if self.mixer.dtype == residual.dtype:
+            return residual, residual
+        x = ctx.shared.get(self.CAST)
+        if x is None:
+            x = ctx.buffer(self.CAST, tuple(residual.shape), self.mixer.dtype)
+            x.copy_(residual)
+            ctx.shared[self.CAST] = x
+        return residual, x
+
+    def _mid_norm(self, ctx, x, branch, norm):
+        """rmsnorm(alpha * x + branch) * gain as float32 and, beside it, as the engine's type."""
+        typed = self.mixer.dtype != x.dtype
+        out = ctx.buffer("postnorm.mid", tuple(x.shape), x.dtype)
+        cast = ctx.buffer("postnorm.mid.cast", tuple(x.shape), self.mixer.dtype) if typed else None
+        norm.k.post_norm(x, materialize(branch), float(self.options.get("alpha", 1.0)), norm.weight, norm.eps, out, cast_out=cast)
+        return out, cast if typed else out
+
+    def forward(self, ctx, residual, delta, call):
+        stream, x = self._enter(ctx, residual, delta)
+        hist = self.stream_mix.history(ctx, stream)             # X_0 is kept before the stream changes
+        mid, mid_x = self._mid_norm(ctx, stream, self.mixer.forward(ctx, x, call), self.mixer_norm)
+        ff = self.feed_forward.forward(ctx, mid_x)
+        alpha = float(self.options.get("alpha", 1.0))
+        typed = self.mixer.dtype != stream.dtype
+        cast = ctx.buffer(self.CAST, tuple(stream.shape), self.mixer.dtype) if typed else None
+        mix, norm = self.stream_mix, self.feed_forward_norm
+        norm.k.post_norm(mid, materialize(ff), alpha, norm.weight, norm.eps, stream, cast_out=cast, history=hist[:mix.inputs], mix=mix.weight)
+        if typed:
+            ctx.shared[self.CAST] = cast
+        return stream, None
+
+
+class PostNormDepthMixerBlock(PostNormDepthBlock):
+    """The same without a feed-forward: X = mixer_norm(alpha * x + mixer(x))."""
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "stream_mix": "stream_mix"}
+
+    def forward(self, ctx, residual, delta, call):
+        stream, x = self._enter(ctx, residual, delta)
+        hist = self.stream_mix.history(ctx, stream)
+        branch = self.mixer.forward(ctx, x, call)
+        typed = self.mixer.dtype != stream.dtype
+        cast = ctx.buffer(self.CAST, tuple(stream.shape), self.mixer.dtype) if typed else None
+        mix, norm = self.stream_mix, self.mixer_norm
+        norm.k.post_norm(stream, materialize(branch), float(self.options.get("alpha", 1.0)), norm.weight, norm.eps, stream, cast_out=cast,
+                         history=hist[:mix.inputs], mix=mix.weight)
+        if typed:
+            ctx.shared[self.CAST] = cast
+        return stream, None

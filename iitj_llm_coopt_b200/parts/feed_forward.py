@@ -94,6 +94,37 @@ class ClampedGLU(Part):
         return self.k.linear(act, self.down, out)
 
 
+class PolyNormMLP(Part):
+    """x -> act(x Wup^T) Wdown^T with a normed polynomial as activation: with N dividing a token's row of inner values by its root
+    mean square (float32 statistics, the spec's option `eps`) and powers taken element by element,
+
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,        (a, b, c, e) the four numbers of the parameter `act`."""
+    graph_safe = True
+
+    def __init__(self, spec, kernels, dtype):
+        self.spec, self.k, self.dtype = spec, kernels, dtype
+        self.width, self.inner, self.eps = spec.width, spec.inner, float(spec.option("eps", 1e-6))
+        self.up = self.down = self.act = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        return {"up": ParamSpec((spec.inner, spec.width)), "down": ParamSpec((spec.width, spec.inner)),
+                "act": ParamSpec((4,), kind="vector")}
+
+    def load(self, tensors: dict) -> None:
+        super().load(tensors)
+        self.act = self.act.float().contiguous()
+
+    def forward(self, ctx, x):
+        t = x.shape[0]
+        z = ctx.buffer("ffn.up", (t, self.inner), self.dtype)
+        self.k.linear(x, self.up, z)
+        act = ctx.buffer("ffn.act", (t, self.inner), self.dtype)
+        self.k.poly_norm(z, self.act, self.eps, act)
+        out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
+        return self.k.linear(act, self.down, out)
+
+
 class RoutedGLU(Part):
     """A mixture of `experts` small ClampedGLU feed-forwards of which each token uses `experts_per_token`.
 
@@ -101,6 +132,8 @@ class RoutedGLU(Part):
         out = sum over the chosen e of s[e] * expert_e(x)            (the weights are not renormalised)
 
     Options of the spec: `router` = "sigmoid" takes s = sigmoid(z) of every output by itself instead of the softmax;
+    `router` = "chosen_softmax" compares the router outputs themselves and takes the softmax over the chosen ones alone as weights
+    (they sum to one); `router_bias` = True adds a stored bias to the router outputs before anything else;
     `correction` = False: there is no stored correction and the choice is by s alone; `expert` = "silu" makes the
     experts plain silu-gated ones, silu(g) * u, instead of the clamped form; `weight_on` = "input" feeds expert e the row
     s[e] * x and sums the experts' outputs as they are, out = sum expert_e(s[e] * x) (the first product being linear in
@@ -122,16 +155,22 @@ class RoutedGLU(Part):
         self.identity = int(spec.option("identity", 0))
         self.limit, self.slope = float(spec.option("limit", 0.0)), float(spec.option("slope", 1.0))
         self.sigmoid = spec.option("router", "softmax") == "sigmoid"
+        self.chosen_softmax = spec.option("router", "softmax") == "chosen_softmax"
+        self.has_router_bias = bool(spec.option("router_bias", False))
+        if self.has_router_bias and not self.chosen_softmax:
+            raise ValueError("routed feed-forward: a router bias goes with router = chosen_softmax")
+        if self.chosen_softmax and spec.option("correction", True):
+            raise ValueError("routed feed-forward: router = chosen_softmax has no correction (correction = False)")
         self.has_correction = bool(spec.option("correction", True))
         self.on_input = spec.option("weight_on", "output") == "input"
         self.silu = spec.option("expert", "clamped") == "silu"
-        if spec.option("router", "softmax") not in ("softmax", "sigmoid") or spec.option("weight_on", "output") not in ("input", "output"):
+        if spec.option("router", "softmax") not in ("softmax", "sigmoid", "chosen_softmax") or spec.option("weight_on", "output") not in ("input", "output"):
             raise ValueError("routed feed-forward: router is softmax or sigmoid, weight_on is input or output")
         if self.on_input and (self.identity or not self.silu):
             raise ValueError("routed feed-forward: weights on the experts' inputs go with plain silu experts and no identity experts")
         if self.silu and not self.on_input:
             raise ValueError("routed feed-forward: plain silu experts are served with the weight on their input")
-        self.router = self.correction = self.expert_gate_up = self.expert_down = None
+        self.router = self.correction = self.router_bias = self.expert_gate_up = self.expert_down = None
         self.prepare_key = f"routed_glu.{self.top}"          # layers with as many choices a token share the step's plan
 
     def _by_expert(self, tokens: int) -> bool:
@@ -154,6 +193,8 @@ class RoutedGLU(Part):
         out = {"router": ParamSpec((outputs, w))}
         if spec.option("correction", True):
             out["correction"] = ParamSpec((outputs,), kind="vector")
+        if spec.option("router_bias", False):
+            out["router_bias"] = ParamSpec((outputs,), kind="vector")
         if e:
             out["expert_gate_up"] = ParamSpec((e * 2 * ff, w), pieces=tuple(
                 (f"e{j}.{name}", ff) for j in range(e) for name in ("gate", "up")))
@@ -164,6 +205,8 @@ class RoutedGLU(Part):
         super().load(tensors)
         if self.has_correction:
             self.correction = self.correction.float().contiguous()
+        if self.has_router_bias:
+            self.router_bias = self.router_bias.float().contiguous()
 
     def forward(self, ctx, x):
         t = x.shape[0]
@@ -171,7 +214,10 @@ class RoutedGLU(Part):
         self.k.linear(x, self.router, scores)
         chosen = ctx.buffer("moe.chosen", (t, self.top), torch.int32)
         weights = ctx.buffer("moe.weights", (t, self.top), torch.float32)
-        self.k.route_topk(scores, self.correction, chosen, weights, sigmoid=self.sigmoid)
+        if self.chosen_softmax:
+            self.k.route_topk(scores, self.router_bias, chosen, weights, chosen_softmax=True)
+        else:
+            self.k.route_topk(scores, self.correction, chosen, weights, sigmoid=self.sigmoid)
         out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
         plan = y = None
         if self.experts:

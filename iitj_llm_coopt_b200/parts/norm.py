@@ -39,3 +39,11 @@ class ScalarGainRMSNorm(RMSNorm):
 
     def load(self, tensors: dict) -> None:
         self.weight = tensors["weight"].float().reshape(1).expand(self.width).contiguous()
+
+
+class OnePlusRMSNorm(RMSNorm):
+    """RMSNorm whose gain is stored around zero: y = x * rsqrt(mean(x^2) + eps) * (1 + w).  One is added once, at loading, in
+    float32, so the kernels of `RMSNorm` serve it."""
+
+    def load(self, tensors: dict) -> None:
+        self.weight = (tensors["weight"].float() + 1.0).contiguous()

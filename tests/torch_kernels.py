@@ -278,7 +278,7 @@ def flat_planes(cache, kv_heads, key_dim, value_dim, shared_value):
 
 
 def ref_attention_flat(q, q_stride_heads, cache, block_table, token_request, positions, heads, kv_heads, key_dim, value_dim,
-                       shared_value, window, scale, gate=None, softcap=0.0, slopes=None, q_temp=None):
+                       shared_value, window, scale, gate=None, softcap=0.0, slopes=None, q_temp=None, sinks=None):
     """q [T, >= heads * key_dim] (query heads first); returns [T, heads * value_dim] float32.  gate [T, heads] or
     [T, heads * value_dim]; score options: tanh squashing at `softcap`, `slopes` [heads] times the distance taken off,
     `q_temp` (coef, every) the query's growth with the logarithm of its position."""
@@ -302,7 +302,10 @@ def ref_attention_flat(q, q_stride_heads, cache, block_table, token_request, pos
             s = softcap * torch.tanh(s / softcap)
         if slopes is not None:
             s = s - slopes.float().view(heads, 1) * (pos - idx).float().view(1, -1)
-        p = torch.softmax(s, dim=-1)
+        if sinks is not None:      # one more term in every row's denominator, without key or value
+            p = torch.softmax(torch.cat([s, sinks.float().view(heads, 1)], dim=1), dim=-1)[:, :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
         o = torch.einsum("hn,nhv->hv", p, v)
         if gate is not None:
             o = o * torch.sigmoid(gate[t].float()).view(heads, -1)
@@ -310,10 +313,109 @@ def ref_attention_flat(q, q_stride_heads, cache, block_table, token_request, pos
     return out.view(T, heads * value_dim)
 
 
-def ref_route_topk(scores, correction, top, sigmoid=False):
+def ref_route_topk(scores, correction, top, sigmoid=False, chosen_softmax=False):
+    if chosen_softmax:             # the outputs (plus their bias) compared as they are; softmax over the chosen alone
+        z = scores.float() + (correction.float() if correction is not None else 0.0)
+        val, chosen = torch.topk(z, top, dim=-1)
+        return chosen.to(torch.int32), torch.softmax(val, dim=-1)
     s = torch.sigmoid(scores.float()) if sigmoid else torch.softmax(scores.float(), dim=-1)
     chosen = torch.topk(s + correction.float() if correction is not None else s, top, dim=-1).indices
     return chosen.to(torch.int32), torch.gather(s, 1, chosen)
+
+
+def ref_qk_prepare(proj, heads, kv_heads, dim, vdim, eps, bias=None, norm="none", q_gain=None, k_gain=None, norm_first=True,
+                   cos=None, sin=None, rotary_dim=0, interleaved=False, own_kv=True, value_from_key=False):
+    """(q [T, H, D], k [T, G, D] or None, v [T, G, V] or None) float32 after bias, norm and rotation in the chosen order."""
+    T = proj.shape[0]
+    x = proj.float()
+    if bias is not None:
+        x = x + bias.float()[:x.shape[1]]
+    qc, kc = heads * dim, kv_heads * dim if own_kv else 0
+    q = x[:, :qc]
+    k = x[:, qc:qc + kc] if own_kv else None
+    v = None
+    if own_kv:
+        v = (k if value_from_key else x[:, qc + kc:]).reshape(T, kv_heads, vdim).clone()
+
+    def normed(z, n, gain):
+        if norm == "none":
+            return z
+        if norm == "row":
+            z = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + eps)
+            return z * gain.float() if gain is not None else z
+        z = z.reshape(T, n, dim)
+        z = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + eps)
+        return (z * gain.float() if gain is not None else z).reshape(T, n * dim)
+
+    def rotated(z, n):
+        if not rotary_dim:
+            return z
+        return ref_rotate(z.reshape(T, n, dim), cos, sin, rotary_dim, interleaved).reshape(T, n * dim)
+
+    def both(z, n, gain):
+        return rotated(normed(z, n, gain), n) if norm_first else normed(rotated(z, n), n, gain)
+
+    q = both(q, heads, q_gain).reshape(T, heads, dim)
+    if own_kv:
+        k = both(k, kv_heads, k_gain).reshape(T, kv_heads, dim)
+    return q, k, v
+
+
+def ref_post_norm(x, branch, alpha, gain, eps):
+    v = alpha * x.float() + branch.float()
+    return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * gain.float()
+
+
+def ref_branch_mean(branches, gains, scale, eps):
+    out = 0.0
+    for b, g in zip(branches, gains):
+        b = b.float()
+        out = out + b * torch.rsqrt(b.pow(2).mean(-1, keepdim=True) + eps) * g.float()
+    return scale * out
+
+
+def ref_poly_norm(z, coef, eps):
+    z = z.float()
+
+    def unit(v):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    a, b, c, e = coef.float().tolist()
+    return a * unit(z) + b * unit(z * z) + c * unit(z * z * z) + e
+
+
+def ref_lru(proj, y_col, x_col, width, bias_y, bias_x, taps_w, conv_bias, ra, ri, ra_bias, ri_bias, lam, decay_scale, state,
+            state_slots, cu_seqlens, write=True):
+    """out [T, width] float32; `state` [slots, taps, width] (row 0 the recurrence, then the convolution's last inputs) is
+    brought up to date when `write`."""
+    T, taps, blocks = proj.shape[0], taps_w.shape[1], ra.shape[0]
+    p = proj.float()
+    y = ref_gelu_tanh(p[:, y_col:y_col + width] + bias_y.float())
+    z = p[:, x_col:x_col + width] + bias_x.float()
+    out = torch.zeros(T, width, dtype=torch.float32, device=proj.device)
+    sp = torch.nn.functional.softplus(lam.float())
+    for r in range(state_slots.shape[0]):
+        lo, hi = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        if hi == lo:
+            continue
+        st = state[int(state_slots[r])]
+        rows = torch.cat([st[1:], z[lo:hi]], dim=0)                # taps - 1 old rows, then the new ones
+        n = hi - lo
+        u = conv_bias.float().expand(n, width).clone()
+        for j in range(taps):
+            u = u + rows[j:j + n] * taps_w.float()[:, j]
+        ub = u.view(n, blocks, width // blocks)
+        gr = torch.sigmoid(torch.einsum("tbi,boi->tbo", ub, ra.float()).reshape(n, width) + ra_bias.float())
+        gi = torch.sigmoid(torch.einsum("tbi,boi->tbo", ub, ri.float()).reshape(n, width) + ri_bias.float())
+        a = torch.exp(-decay_scale * gr * sp)
+        b = torch.sqrt(torch.clamp(1.0 - a * a, min=0.0)) * gi * u
+        S = st[0].clone()
+        for t in range(n):
+            S = a[t] * S + b[t]
+            out[lo + t] = S * y[lo + t]
+        if write:
+            st[0] = S
+            st[1:] = rows[rows.shape[0] - (taps - 1):]
+    return out
 
 
 def ref_token_shift(x, mu, before, state_slots, cu_seqlens):
@@ -538,13 +640,53 @@ class TorchKernels:
                 vplane[p, :, o, :] = v[t].to(cache.dtype)
 
     def attention_flat(self, q, cache, meta, out, heads, kv_heads, key_dim, value_dim, shared_value=False, window=0, scale=1.0,
-                       gate=None, plan=None, softcap=0.0, slopes=None, q_temp=None):
+                       gate=None, plan=None, softcap=0.0, slopes=None, q_temp=None, sinks=None):
         out.copy_(ref_attention_flat(q, None, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
-                                     key_dim, value_dim, shared_value, window, scale, gate, softcap, slopes, q_temp))
+                                     key_dim, value_dim, shared_value, window, scale, gate, softcap, slopes, q_temp, sinks))
         return out
 
-    def route_topk(self, scores, correction, chosen, weights, sigmoid=False):
-        c, w = ref_route_topk(scores, correction, chosen.shape[1], sigmoid)
+    def qk_prepare(self, proj, heads, kv_heads, dim, vdim, eps, cache_layer=None, slots=None, bias=None, norm="none", q_gain=None,
+                   k_gain=None, norm_first=True, tables=None, rotary_dim=0, interleaved=False, own_kv=True, value_from_key=False):
+        cos, sin = tables if rotary_dim else (None, None)
+        q, k, v = ref_qk_prepare(proj, heads, kv_heads, dim, vdim, eps, bias, norm, q_gain, k_gain, norm_first, cos, sin, rotary_dim,
+                                 interleaved, own_kv, value_from_key)
+        T = proj.shape[0]
+        proj[:, :heads * dim] = q.reshape(T, -1).to(proj.dtype)
+        if slots is not None:
+            kplane, vplane, ps = flat_planes(cache_layer, kv_heads, dim, vdim, False)
+            for t in range(T):
+                p, o = divmod(int(slots[t]), ps)
+                kplane[p, :, o, :] = k[t].to(cache_layer.dtype)
+                vplane[p, :, o, :] = v[t].to(cache_layer.dtype)
+        return proj
+
+    def post_norm(self, x, branch, alpha, gain, eps, out, cast_out=None, history=None, mix=None):
+        y = ref_post_norm(x, branch, alpha, gain, eps)
+        if history is not None:
+            n = mix.shape[0]
+            history[n - 1] = y
+            y = (mix.float().view(n, 1, 1) * history[:n]).sum(0)
+        out.copy_(y)
+        if cast_out is not None:
+            cast_out.copy_(y)
+        return out
+
+    def branch_mean(self, branches, gains, scale, eps, out):
+        out.copy_(ref_branch_mean(branches, gains, scale, eps))
+        return out
+
+    def poly_norm(self, z, coef, eps, act):
+        act.copy_(ref_poly_norm(z, coef, eps))
+        return act
+
+    def lru(self, proj, y_col, x_col, width, bias_y, bias_x, taps_w, conv_bias, ra, ri, ra_bias, ri_bias, lam, decay_scale, state,
+            state_slots, token_request, cu_seqlens, out, longest, write=True):
+        out.copy_(ref_lru(proj, y_col, x_col, width, bias_y, bias_x, taps_w, conv_bias, ra, ri, ra_bias, ri_bias, lam, decay_scale,
+                          state, state_slots, cu_seqlens, write))
+        return out
+
+    def route_topk(self, scores, correction, chosen, weights, sigmoid=False, chosen_softmax=False):
+        c, w = ref_route_topk(scores, correction, chosen.shape[1], sigmoid, chosen_softmax)
         chosen.copy_(c)
         weights.copy_(w)
 
