@@ -246,3 +246,11 @@ def forward(cfg, w, tokens, want_layers=False):
         handed.append(x)
     logits = (unit_rms(x, eps) * (1.0 + w["final.norm"])) @ w["head"].T
     return (logits, torch.stack(handed)) if want_layers else logits
+
+
+def greedy(cfg, w, prompt, n):
+    """n tokens chosen by the largest logit, each fed back."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
