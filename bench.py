@@ -2,7 +2,7 @@
 """Headline benchmark: decode tokens/s and prefill tokens/s of the Llama 3.1 8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
-    python bench.py --family lifusun|rodapel|fomerax [--shape 8b|3b|1b|toy]     (another family beside Llama at equal layer sizes)
+    python bench.py --family lifusun|rodapel|fomerax|mamusun [--shape 8b|3b|1b|toy]     (another family beside Llama at equal layer sizes)
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default 8)
 with `context` tokens per request already in the cache, timed on the device with one pair
@@ -150,9 +150,9 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase alone with few repetitions and print a short line (for profilers)")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself (for profiling)")
-    ap.add_argument("--family", choices=["lifusun", "rodapel", "fomerax"], default=None,
+    ap.add_argument("--family", choices=["lifusun", "rodapel", "fomerax", "mamusun"], default=None,
                     help="instead of the headline line: prefill and decode of this family at the layer sizes of --shape "
-                         "(8b, 3b, 1b, toy; eight layers) beside a Llama of the same sizes and depth (fomerax: also beside the "
+                         "(8b, 3b, 1b, toy; eight layers) beside a Llama of the same sizes and depth (fomerax and mamusun: also beside the "
                          "Rodapel of those sizes), and its kernels alone")
     args = ap.parse_args()
     if args.family:

@@ -238,7 +238,7 @@ def run_workload(engine, reqs, offsets, temperature=0.0, max_concurrency=None, s
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", help="folder with config.json and safetensors weights")
-    ap.add_argument("--shape", help="in place of --model: a named shape with random weights (8b, 3b, 1b, tinyA, tinyB, and the other families at those layer sizes: lifusun-8b, rodapel-1b, fomerax-toy, ...)")
+    ap.add_argument("--shape", help="in place of --model: a named shape with random weights (8b, 3b, 1b, tinyA, tinyB, and the other families at those layer sizes: lifusun-8b, rodapel-1b, fomerax-toy, mamusun-3b, ...)")
     ap.add_argument("--random-seed", type=int, default=None, help="seed of the random weights of --shape")
     ap.add_argument("--workload", required=True,
                     help="JSONL file of requests, synthetic:N:PMIN-PMAX:OMIN-OMAX, baseline:1b-continuous or baseline:3b-mixed")

@@ -12,6 +12,7 @@
 //
 // llm_lru_conv:   u (float32 [tokens, width]) from proj and the state's rows of z.
 // llm_lru_gates:  a and b = sqrt(1 - a^2) i u (float32 [tokens, width]) from u; FMA tiles with a fixed order along k.
+// llm_lru_step:   all three at once for a step in which every request brings one token.
 // llm_lru_scan:   the recurrence, out, and the new state.  Short portions: one thread per (request, channel) walks the tokens.
 //                 Long portions are cut into segments of kSegment tokens: every segment's (product of a, end value from zero)
 //                 first, then the segments' starting values one after the other, then every segment again from its start.
@@ -48,8 +49,34 @@ lru_conv_kernel(const T* __restrict__ proj, int ld, int x_col, const float* __re
     }
 }
 
-constexpr int GT = 32, GN = 64, GK = 32;       // tokens x outputs of a block's tile, and the k chunk
+constexpr int GT = 64, GN = 128, GK = 16;      // tokens x outputs of a block's tile, and the k chunk
+constexpr int GPAD = 4;                        // shared rows padded so that the transposing stores spread over the banks
 
+// Eight neighbouring numbers as float32: one 16-byte read of bfloat16, two of float32 (`vec`: the address allows it), else one by one;
+// numbers from `n` on read as zero.
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, int n, bool vec, float (&v)[8]) {
+    if (vec && n >= 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = j < n ? __bfloat162float(p[j]) : 0.f;
+    }
+}
+__device__ __forceinline__ void load8(const float* p, int n, bool vec, float (&v)[8]) {
+    if (vec && n >= 8) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = j < n ? p[j] : 0.f;
+    }
+}
+
+// Both gate products as FMA tiles: a thread holds 8 tokens x 4 outputs of each matrix; operands pass through shared memory with k as
+// the slow index, so that a thread's tokens and outputs are neighbours (float4 reads); the sum along k runs in its natural order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 lru_gates_kernel(const float* __restrict__ u, const T* __restrict__ ra, const T* __restrict__ ri, const float* __restrict__ ra_bias,
@@ -57,50 +84,70 @@ lru_gates_kernel(const float* __restrict__ u, const T* __restrict__ ra, const T*
                  float* __restrict__ b_out, int tokens, int width, int blocks) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float us[GT][GK + 1];
-    __shared__ float was[GN][GK + 1];
-    __shared__ float wis[GN][GK + 1];
+    __shared__ __align__(16) float us[GK][GT + GPAD];
+    __shared__ __align__(16) float was[GK][GN + GPAD];
+    __shared__ __align__(16) float wis[GK][GN + GPAD];
     const int bs = width / blocks;
     const int col_tiles = (bs + GN - 1) / GN;
     const int blk = blockIdx.y / col_tiles, n0 = (blockIdx.y % col_tiles) * GN;
     const int t0 = blockIdx.x * GT;
-    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;      // outputs tx and tx + 32; tokens ty, ty + 8, ty + 16, ty + 24
-    float accr[4][2], acci[4][2];
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;      // outputs 4 tx .. 4 tx + 3; tokens 8 ty .. 8 ty + 7
+    float accr[8][4], acci[8][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { accr[i][0] = accr[i][1] = acci[i][0] = acci[i][1] = 0.f; }
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) accr[i][j] = acci[i][j] = 0.f;
     const T* wa = ra + (size_t)blk * bs * bs;
     const T* wi = ri + (size_t)blk * bs * bs;
+    const bool wvec = bs % 8 == 0 && !((uintptr_t)ra & 15) && !((uintptr_t)ri & 15);
+    const bool uvec = width % 4 == 0 && bs % 4 == 0 && !((uintptr_t)u & 15);
     for (int k0 = 0; k0 < bs; k0 += GK) {
-        for (int i = threadIdx.x; i < GT * GK; i += 256) {
-            const int r = i / GK, k = i % GK;
-            us[r][k] = (t0 + r < tokens && k0 + k < bs) ? u[(size_t)(t0 + r) * width + blk * bs + k0 + k] : 0.f;
+        {   // u: one run of four k per thread
+            const int r = threadIdx.x / 4, kq = (threadIdx.x % 4) * 4;
+            const int left = t0 + r < tokens ? bs - (k0 + kq) : 0;
+            const float* p = u + (size_t)(t0 + r) * width + blk * bs + k0 + kq;
+            float v[4];
+            if (uvec && left >= 4) { const float4 f = *reinterpret_cast<const float4*>(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+            else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = j < left ? p[j] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) us[kq + j][r] = v[j];
         }
-        for (int i = threadIdx.x; i < GN * GK; i += 256) {
-            const int r = i / GK, k = i % GK;
-            const bool ok = n0 + r < bs && k0 + k < bs;
-            was[r][k] = ok ? to_f32(wa[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
-            wis[r][k] = ok ? to_f32(wi[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+        {   // both matrices: one run of eight k of one output row per thread
+            const int r = threadIdx.x / 2, kg = (threadIdx.x % 2) * 8;
+            const int left = n0 + r < bs ? bs - (k0 + kg) : 0;
+            float va[8], vi[8];
+            load8(wa + (size_t)(n0 + r) * bs + k0 + kg, left, wvec, va);
+            load8(wi + (size_t)(n0 + r) * bs + k0 + kg, left, wvec, vi);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { was[kg + j][r] = va[j]; wis[kg + j][r] = vi[j]; }
         }
         __syncthreads();
-#pragma unroll 8
-        for (int k = 0; k < GK; ++k) {
-            const float a0 = was[tx][k], a1 = was[tx + 32][k], i0 = wis[tx][k], i1 = wis[tx + 32][k];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float uv = us[ty + 8 * i][k];
-                accr[i][0] = fmaf(uv, a0, accr[i][0]);
-                accr[i][1] = fmaf(uv, a1, accr[i][1]);
-                acci[i][0] = fmaf(uv, i0, acci[i][0]);
-                acci[i][1] = fmaf(uv, i1, acci[i][1]);
-            }
+        for (int k = 0; k < GK; ++k) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&was[k][4 * tx]);
+            const float4 i4 = *reinterpret_cast<const float4*>(&wis[k][4 * tx]);
+            const float4 u0 = *reinterpret_cast<const float4*>(&us[k][8 * ty]);
+            const float4 u1 = *reinterpret_cast<const float4*>(&us[k][8 * ty + 4]);
+            const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    accr[i][j] = fmaf(uv[i], av[j], accr[i][j]);
+                    acci[i][j] = fmaf(uv[i], iv[j], acci[i][j]);
+                }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int t = t0 + ty + 8 * i, n = n0 + tx + 32 * j;
+        for (int j = 0; j < 4; ++j) {
+            const int t = t0 + 8 * ty + i, n = n0 + 4 * tx + j;
             if (t >= tokens || n >= bs) continue;
             const int c = blk * bs + n;
             const float r = 1.0f / (1.0f + expf(-(accr[i][j] + ra_bias[c])));
@@ -148,6 +195,78 @@ lru_scan_walk_kernel(const float* __restrict__ a, const float* __restrict__ b, c
     if (write && end > start) {
         st[c] = S;
         lru_shift_state(st, proj, ld, x_col, bias_x, taps, start, end, width, c);
+    }
+}
+
+// A step in which every request brings one token: convolution, gates, recurrence and the new state in one kernel.  One block per
+// (request, gate block): it holds the block's u in shared memory, a warp per output row walks k with its lanes (a fixed order), and
+// since no other block reads this block's channels of the state, it brings them up to date itself.
+template <typename T>
+__global__ void __launch_bounds__(512)
+lru_step_kernel(const T* __restrict__ proj, int ld, int y_col, int x_col, const float* __restrict__ bias_y, const float* __restrict__ bias_x,
+                const float* __restrict__ taps_w, const float* __restrict__ conv_bias, int taps, const T* __restrict__ ra,
+                const T* __restrict__ ri, const float* __restrict__ ra_bias, const float* __restrict__ ri_bias, const float* __restrict__ lam,
+                float decay_scale, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
+                T* __restrict__ out, int width, int blocks, int write) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float step_u[];
+    const int bs = width / blocks, blk = blockIdx.x, r = blockIdx.y;
+    const int t = cu_seqlens[r];
+    if (cu_seqlens[r + 1] <= t) return;                    // the request brings nothing: the whole block leaves
+    float* st = state + (size_t)state_slots[r] * taps * width;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = threadIdx.x; c < bs; c += blockDim.x) {
+        const int ch = blk * bs + c;
+        const float z = to_f32(proj[(size_t)t * ld + x_col + ch]) + (bias_x ? bias_x[ch] : 0.f);
+        float acc = conv_bias ? conv_bias[ch] : 0.f;
+        for (int j = 0; j + 1 < taps; ++j) acc = fmaf(taps_w[(size_t)ch * taps + j], st[(size_t)(1 + j) * width + ch], acc);
+        step_u[c] = fmaf(taps_w[(size_t)ch * taps + taps - 1], z, acc);
+    }
+    __syncthreads();
+    const T* wa = ra + (size_t)blk * bs * bs;
+    const T* wi = ri + (size_t)blk * bs * bs;
+    const bool vec = bs % 8 == 0 && !((uintptr_t)ra & 15) && !((uintptr_t)ri & 15);
+    const int nwarp = blockDim.x >> 5;
+    for (int n0 = warp * 4; n0 < bs; n0 += nwarp * 4) {      // four rows a warp at a time, a lane takes runs of eight k
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, si[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = lane * 8; k < bs; k += 256) {
+            float uv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) uv[j] = k + j < bs ? step_u[k + j] : 0.f;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if (n0 + r >= bs) continue;
+                float va[8], vi[8];
+                load8(wa + (size_t)(n0 + r) * bs + k, bs - k, vec, va);
+                load8(wi + (size_t)(n0 + r) * bs + k, bs - k, vec, vi);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { sa[r] = fmaf(uv[j], va[j], sa[r]); si[r] = fmaf(uv[j], vi[j], si[r]); }
+            }
+        }
+        float ma = 0.f, mi = 0.f;                            // lane r keeps row n0 + r
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float ta = warp_sum(sa[r]), ti = warp_sum(si[r]);
+            if (lane == r) { ma = ta; mi = ti; }
+        }
+        const int n = n0 + lane;
+        if (lane < 4 && n < bs) {
+            const int ch = blk * bs + n;
+            const float g = 1.0f / (1.0f + expf(-(ma + ra_bias[ch])));
+            const float gi = 1.0f / (1.0f + expf(-(mi + ri_bias[ch])));
+            const float l = lam[ch];
+            const float a = expf(-decay_scale * g * (l > 20.f ? l : log1pf(expf(l))));
+            const float S = fmaf(a, st[ch], sqrtf(fmaxf(1.0f - a * a, 0.f)) * gi * step_u[n]);
+            out[(size_t)t * width + ch] = from_f32<T>(S * gelu_tanh_lru(to_f32(proj[(size_t)t * ld + y_col + ch]) + (bias_y ? bias_y[ch] : 0.f)));
+            if (write) st[ch] = S;
+        }
+    }
+    if (!write) return;
+    for (int c = threadIdx.x; c < bs; c += blockDim.x) {   // every read of these rows lies before the barrier above
+        const int ch = blk * bs + c;
+        for (int j = 1; j + 1 < taps; ++j) st[(size_t)j * width + ch] = st[(size_t)(j + 1) * width + ch];
+        if (taps > 1) st[(size_t)(taps - 1) * width + ch] = to_f32(proj[(size_t)t * ld + x_col + ch]) + (bias_x ? bias_x[ch] : 0.f);
     }
 }
 
@@ -284,6 +403,28 @@ LLM_API int llm_lru_scan(const float* a, const float* b, const void* proj, int l
         llm_launch(lru_segment_apply_kernel<T>, dim3(cb, (unsigned)(requests * segments)), 128, 0, stream, a, b, (const float*)seg_b,
                    (const T*)proj, ld, y_col, bias_y, cu_seqlens, (T*)out, width, segments);
         LLM_CHECK_LAUNCH("lru_segment_apply");
+        return 0;
+    });
+}
+
+// A step of single tokens (every request brings one, or none): all of the above in one launch.  Sizes as in the three entry points.
+LLM_API int llm_lru_step(const void* proj, int ld, int y_col, int x_col, const float* bias_y, const float* bias_x, const float* taps_w,
+                         const float* conv_bias, int taps, const void* ra, const void* ri, const float* ra_bias, const float* ri_bias,
+                         const float* lam, float decay_scale, float* state, const int* state_slots, const int* cu_seqlens, void* out,
+                         int dtype, int requests, int width, int blocks, int write, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    if (taps < 1 || taps > 9) LLM_FAIL(-1, "lru_step: %d taps (1 to 9)", taps);
+    if (blocks < 1 || width % blocks) LLM_FAIL(-1, "lru_step: width %d is not a multiple of %d blocks", width, blocks);
+    if (requests > 65535) LLM_FAIL(-1, "lru_step: too many requests");
+    const size_t smem = (size_t)(width / blocks) * sizeof(float);
+    if (smem > 200 * 1024) LLM_FAIL(-1, "lru_step: a gate block of %d channels does not fit shared memory", width / blocks);
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(lru_step_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        llm_launch(lru_step_kernel<T>, dim3((unsigned)blocks, (unsigned)requests), 512, smem, stream, (const T*)proj, ld, y_col, x_col, bias_y,
+                   bias_x, taps_w, conv_bias, taps, (const T*)ra, (const T*)ri, ra_bias, ri_bias, lam, decay_scale, state, state_slots,
+                   cu_seqlens, (T*)out, width, blocks, write);
+        LLM_CHECK_LAUNCH("lru_step");
         return 0;
     });
 }

@@ -17,7 +17,7 @@ constexpr int kThreads = 256;
 template <typename TB, typename TC>
 __global__ void __launch_bounds__(kThreads)
 post_norm_kernel(const float* x, const TB* __restrict__ branch, float alpha, const float* __restrict__ gain, float eps,
-                 float* out, TC* __restrict__ cast, float* __restrict__ history, const float* __restrict__ mix,
+                 float* out, TC* __restrict__ cast, float* history, const float* __restrict__ mix,
                  int inputs, long long entry_stride, int width) {
     pdl_trigger();
     pdl_wait();
@@ -31,16 +31,38 @@ post_norm_kernel(const float* x, const TB* __restrict__ branch, float alpha, con
         ss += v * v;
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += kThreads) {
-        float y = pn_row[i] * inv * gain[i];
-        if (history) {
-            history[(size_t)(inputs - 1) * entry_stride + base + i] = y;
-            float m = 0.f;
-            for (int j = 0; j + 1 < inputs; ++j) m = fmaf(mix[j], history[(size_t)j * entry_stride + base + i], m);
-            y = fmaf(mix[inputs - 1], y, m);
+    if (!history) {
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            const float y = pn_row[i] * inv * gain[i];
+            out[base + i] = y;
+            if (cast) cast[base + i] = from_f32<TC>(y);
         }
-        out[base + i] = y;
-        if (cast) cast[base + i] = from_f32<TC>(y);
+        return;
+    }
+    // the earlier entries are only read and the last one only written: the reads of four columns run side by side
+    const float* __restrict__ earlier = history;
+    float* __restrict__ last = history + (size_t)(inputs - 1) * entry_stride;
+    const float w_last = mix[inputs - 1];
+    for (int i0 = threadIdx.x; i0 < width; i0 += 4 * kThreads) {
+        float m[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j + 1 < inputs; ++j) {
+            const float wj = mix[j];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = i0 + e * kThreads;
+                if (i < width) m[e] = fmaf(wj, earlier[(size_t)j * entry_stride + base + i], m[e]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = i0 + e * kThreads;
+            if (i >= width) continue;
+            const float y = pn_row[i] * inv * gain[i];
+            last[base + i] = y;
+            const float mixed = fmaf(w_last, y, m[e]);
+            out[base + i] = mixed;
+            if (cast) cast[base + i] = from_f32<TC>(mixed);
+        }
     }
 }
 

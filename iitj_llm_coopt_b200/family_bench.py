@@ -531,6 +531,154 @@ def _kernels_alone_fomerax(cfg, rod, tokens, batch, context, hbm_gbs, flush):
     return out
 
 
+def _kernels_alone_mamusun(cfg, rod, tokens, batch, context, hbm_gbs, flush):
+    """The kernels and kernel options that Mamusun brought, alone at the shapes of a `tokens`-token prompt and of a decode step of
+    `batch` requests, each beside the like kernel as Rodapel runs it at the same shape: microseconds, the bytes that must move and
+    the fraction of the copy bandwidth that is, or for arithmetic-bound kernels the TFLOP/s."""
+    import torch
+
+    from . import kernels as _k
+    from .parts.base import StepShape
+    from .parts.flat_tiles import plan_flat_tiles
+    K = _k.load()
+    dev, bf = "cuda", torch.bfloat16
+    sink = next(l["mixer"] for l in cfg["layers"] if l["type"] == "attention_2")
+    att = next(l["mixer"] for l in cfg["layers"] if l["type"] == "attention")
+    par = next(l["mixer"] for l in cfg["layers"] if l["type"] == "parallel")
+    moe = next(l["mlp"] for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
+    dense = next(l["mlp"] for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "dense")
+    width, n_layers = cfg["width"], len(cfg["layers"])
+    H, G, D, window = att["heads"], att["kv_heads"], att["dim"], att["mask"]["size"]
+    rot = par["left"]["rot"]["dims"]
+    inner, blocks, taps = par["right"]["width"], par["right"]["blocks"], par["right"]["conv"]
+    page = 16
+    out = []
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def record(name, us, nbytes=None, flops=None, like=None):
+        r = {"kernel": name, "us": round(us, 2)}
+        if nbytes is not None:
+            r.update(mbytes=round(nbytes / 1e6, 2), frac_of_copy_bandwidth=round(nbytes / (us * 1e-6) / (hbm_gbs * 1e9), 3))
+        if flops is not None:
+            r.update(tflops=round(flops / (us * 1e-6) / 1e12, 1))
+        if like:
+            r["like"] = like
+        out.append(r)
+
+    for label, T, B, per in (("prefill", tokens, 1, tokens), ("decode", batch, batch, 1)):
+        ctx_len = per if label == "prefill" else context
+        pages_per = -(-ctx_len // page)
+        treq = [b for b in range(B) for _ in range(per)]
+        pos = [ctx_len - per + i for _ in range(B) for i in range(per)]
+        table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+        slots = i32([int(table[b, p // page]) * page + p % page for b, p in zip(treq, pos)])
+        meta = SimpleNamespace(block_table=table, token_request=i32(treq), positions=i32(pos), query_lens=[per] * B,
+                               seq_lens_host=[ctx_len] * B, attention_plan=None)
+
+        def plan_for(win):
+            plan = plan_flat_tiles(K, StepShape([per] * B, [ctx_len] * B, T, label == "decode", False, dev), H, G, D, D, win)
+            plan.bind({"tiles": i32(plan.arrays["tiles"])})
+            return plan
+        causal = sum(p + 1 for p in pos)
+        seen = sum(min(p + 1, window) for p in pos)
+        # --- between the projection and the scores: the three forms beside the head norms with store
+        cache = (torch.randn(B * pages_per + 1, G * page * 2 * D, device=dev) * 0.5).to(bf)
+        qkv = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+        qk = torch.randn(T, (H + G) * D, device=dev).to(bf)
+        gains_h = torch.ones(D, device=dev)
+        gq, gk, bias = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev), torch.zeros((H + G) * D, device=dev)
+        ang = torch.tensor(pos, device=dev).float().unsqueeze(1) * (1.0 / 1e4 ** (torch.arange(D // 2, device=dev).float() / (D // 2)))
+        full = (ang.cos().contiguous(), ang.sin().contiguous())
+        part = (full[0][:, :rot // 2].contiguous(), full[1][:, :rot // 2].contiguous())
+        moved = T * ((2 * H + 2 * G) * D + G * D) * 2
+        like = f"headnorm_store ({label})"
+        us = 1e3 * _timed(lambda: K.qk_prepare(qk, H, G, D, D, 1e-6, cache_layer=cache, slots=slots, bias=bias, norm="row", q_gain=gq, k_gain=gk,
+                                               tables=full, rotary_dim=D, value_from_key=True), 10, 3, flush)
+        record(f"qk_prepare: bias, norm of the whole projection, halves rotate, keys as values ({label})", us, nbytes=moved, like=like)
+        us = 1e3 * _timed(lambda: K.qk_prepare(qkv, H, G, D, D, 1e-6, cache_layer=cache, slots=slots, norm="head", norm_first=False, tables=part,
+                                               rotary_dim=rot, interleaved=True), 10, 3, flush)
+        record(f"qk_prepare: neighbours rotate, then unit head norms ({label})", us, nbytes=moved, like=like)
+        us = 1e3 * _timed(lambda: K.qk_prepare(qkv[:, :H * D].contiguous(), H, G, D, D, 1e-6, norm="head", q_gain=gains_h, own_kv=False), 10, 3, flush)
+        record(f"qk_prepare: head norms of queries alone ({label})", us, nbytes=T * 2 * H * D * 2, like=like)
+        us = 1e3 * _timed(lambda: K.headnorm_store(qkv, gains_h, gains_h, 1e-6, cache, slots, H, G, D, D), 10, 3, flush)
+        record(like, us, nbytes=moved)
+        # --- the sink in the softmax, causal; the window beside it
+        ao = torch.empty(T, H * D, device=dev, dtype=bf)
+        sinks = torch.zeros(H, device=dev)
+        for name, win, kw, lk in ((f"attention_flat with sinks ({label})", 0, dict(sinks=sinks), f"attention_flat, plain scores ({label})"),
+                                  (f"attention_flat, plain scores ({label})", 0, {}, None),
+                                  (f"attention_flat, window {window} ({label})", window, {}, None)):
+            plan = plan_for(win)
+            us = 1e3 * _timed(lambda: K.attention_flat(qkv, cache, meta, ao, H, G, D, D, scale=D ** -0.5, window=win, plan=plan, **kw), 5, 3, flush)
+            if label == "decode":
+                record(name, us, nbytes=B * (min(ctx_len, win) if win else ctx_len) * G * 2 * D * 2, like=lk)
+            else:
+                record(name, us, flops=2 * (seen if win else causal) * H * 2 * D, like=lk)
+        # --- norms behind the sums, the average over depth, the mean of normed branches; beside the branch norm
+        x = torch.randn(T, width, device=dev)
+        branch = torch.randn(T, width, device=dev).to(bf)
+        nw = torch.ones(width, device=dev)
+        mid, cast = torch.empty(T, width, device=dev), torch.empty(T, width, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.post_norm(x, branch, 3.0, nw, 1e-6, mid, cast_out=cast), 10, 3, flush)
+        record(f"post_norm ({label})", us, nbytes=T * width * (4 + 2 + 4 + 2), like=f"norm_add ({label})")
+        hist = torch.randn(n_layers + 1, T, width, device=dev)
+        mix = torch.ones(n_layers + 1, device=dev) / (n_layers + 1)
+        us = 1e3 * _timed(lambda: K.post_norm(mid, branch, 3.0, nw, 1e-6, x, cast_out=cast, history=hist, mix=mix), 10, 3, flush)
+        record(f"post_norm with the average over {n_layers + 1} entries ({label})", us, nbytes=T * width * (4 + 2 + 4 + 2 + 4 * (n_layers + 1)),
+               like=f"norm_add ({label})")
+        b2 = torch.randn(T, width, device=dev).to(bf)
+        fo = torch.empty(T, width, device=dev)
+        us = 1e3 * _timed(lambda: K.branch_mean([branch, b2], [nw, nw], 0.5, 1e-6, fo), 10, 3, flush)
+        record(f"branch_mean of two ({label})", us, nbytes=T * width * (2 + 2 + 4), like=f"norm_add ({label})")
+        us = 1e3 * _timed(lambda: K.norm_add(x, branch, nw, 1e-6, cast_out=cast), 10, 3, flush)
+        record(f"norm_add ({label})", us, nbytes=T * width * (2 + 4 + 4 + 2))
+        # --- the normed polynomial beside the clamped gate
+        ff = dense["ff"]
+        z = torch.randn(T, ff, device=dev).to(bf)
+        act = torch.empty(T, ff, device=dev, dtype=bf)
+        coef = torch.tensor([0.8, 0.5, 0.3, 0.1], device=dev)
+        us = 1e3 * _timed(lambda: K.poly_norm(z, coef, 1e-6, act), 10, 3, flush)
+        record(f"poly_norm ({label})", us, nbytes=T * ff * 2 * 2, like=f"glu_clamped ({label})")
+        gu = torch.randn(T, 2 * ff, device=dev).to(bf)
+        us = 1e3 * _timed(lambda: K.glu_clamped(gu, act, 7.0, 1.702), 10, 3, flush)
+        record(f"glu_clamped ({label})", us, nbytes=T * ff * 2 * 3)
+        # --- the gated recurrence with its convolution and gates, beside Rodapel's wkv walk
+        side = inner // blocks
+        proj = torch.randn(T, 2 * inner, device=dev).to(bf)
+        vec = [torch.zeros(inner, device=dev) for _ in range(6)]
+        tw = torch.randn(inner, taps, device=dev) * 0.5
+        ra = (torch.randn(blocks, side, side, device=dev) * side ** -0.5).to(bf)
+        ri = (torch.randn(blocks, side, side, device=dev) * side ** -0.5).to(bf)
+        state = torch.zeros(B, taps, inner, device=dev)
+        sl, cu = i32(list(range(B))), i32([per * b for b in range(B + 1)])
+        lo = torch.empty(T, inner, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.lru(proj, 0, inner, inner, vec[0], vec[1], tw, vec[2], ra, ri, vec[3], vec[4], vec[5], 8.0, state, sl,
+                                        i32(treq), cu, lo, longest=per), 5, 3, flush)
+        record(f"lru: convolution, gates and recurrence ({label})", us, nbytes=T * inner * 6 + 2 * ra.numel() * 2 + B * taps * inner * 8,
+               flops=4 * T * inner * side, like=f"wkv_scan ({label})")
+        rmix = next(l["mixer"] for l in rod["layers"] if l["type"] == "wkv")
+        rheads, rdim = rmix["heads"], rmix["dim"]
+        rn = rheads * rdim
+        rkvg = torch.randn(4 * T, rn, device=dev).to(bf)
+        decay = torch.rand(T, rn, device=dev)
+        wstate = torch.zeros(B, rheads, rdim, rdim, device=dev)
+        wo = torch.empty(T, rn, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.wkv_scan(rkvg, decay, torch.zeros(rheads, rdim, device=dev), torch.ones(rn, device=dev), 1e-6, wstate, sl, cu, wo,
+                                             rheads, rdim), 5, 3, flush)
+        record(f"wkv_scan ({label})", us, nbytes=T * rn * (8 + 4 + 2) + B * rn * rdim * 8)
+        # --- routing by a softmax over the chosen
+        E, top = moe["router"]["experts"], moe["router"]["top"]
+        scores, rb = torch.randn(T, E, device=dev), torch.zeros(E, device=dev)
+        chosen, wts = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, device=dev)
+        us = 1e3 * _timed(lambda: K.route_topk(scores, rb, chosen, wts, chosen_softmax=True), 10, 3, flush)
+        record(f"route_topk, softmax over the chosen ({label})", us, like=f"route_topk, softmax ({label})")
+        us = 1e3 * _timed(lambda: K.route_topk(scores, rb, chosen, wts), 10, 3, flush)
+        record(f"route_topk, softmax ({label})", us)
+    return out
+
+
 def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_source) -> dict:
     import torch
 
@@ -545,13 +693,14 @@ def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_
     t0 = time.time()
     rows = [_model_runs(f"{family}-{shape}", lif, lif["vocab"], batch, context, steps, warmup, prefill_tokens, flush)]
     beside = None
-    if family == "fomerax":          # the closest family stands beside it too: latent and windowed attention, routed experts
+    if family in ("fomerax", "mamusun"):          # the closest family stands beside it too: windowed attention, a recurrence, routed experts
         _, beside = SHAPES[f"rodapel-{shape}"]
         rows.append(_model_runs(f"rodapel-{shape}", beside, beside["vocab"], batch, context, steps, warmup, prefill_tokens, flush))
     rows.append(_model_runs(f"{llama_name} cut to {len(lif['layers'])} layers", llama, llama["vocab_size"], batch, context, steps, warmup,
                             prefill_tokens, flush))
-    alone = {"lifusun": _kernels_alone_lifusun, "rodapel": _kernels_alone_rodapel, "fomerax": _kernels_alone_fomerax}[family](
-        lif, beside if family == "fomerax" else llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
+    alone = {"lifusun": _kernels_alone_lifusun, "rodapel": _kernels_alone_rodapel, "fomerax": _kernels_alone_fomerax,
+             "mamusun": _kernels_alone_mamusun}[family](
+        lif, beside if beside is not None else llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
     return {"family": family, "shape": shape, "dtype": "bf16", "data": "synthetic (random weights, random tokens)",
             "models": rows, "kernels_alone": alone, "copy_bandwidth_gbs": peaks["hbm_gbs"], "peaks": f"of {source}",
             "l2": "256 MB written between timed runs", "steps": steps, "warmup": warmup, "seconds": round(time.time() - t0, 1)}

@@ -133,6 +133,9 @@ _SIGNATURES = {
                      _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "llm_lru_gates": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int,
                       _c_int, _c_int, _c_int, _c_void_p],
+    "llm_lru_step": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                     _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                     _c_void_p],
     "llm_lru_scan": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
                      _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "llm_gemm_grouped_tile_rows": [],
@@ -355,6 +358,7 @@ class Kernels:
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         self.flat_mma = os.environ.get("IITJ_FLAT_MMA", "1") != "0"                     # tensor-core attention over flat pages
         self.talking_mma = os.environ.get("IITJ_TALKING_MMA", "1") != "0"               # tensor-core talking attention for prompt portions
+        self.lru_step = os.environ.get("IITJ_LRU_STEP", "1") != "0"                      # one-launch recurrence for steps of single tokens
         self.retention_blocks = int(os.environ.get("IITJ_RETENTION_BLOCKS", "0"))        # blocks the retention walk aims at (0: its own rule)
         self.retention_segments = int(os.environ.get("IITJ_RETENTION_SEGMENTS", "0"))    # 1: never in segments, 2: always
         if os.environ.get("IITJ_PDL", "1") == "0":
@@ -1262,10 +1266,16 @@ class Kernels:
             _check(t, "lru." + name, torch.int32, 1)
         requests = state_slots.shape[0]
         _need(token_request.shape[0] == tokens and cu_seqlens.shape[0] == requests + 1, "lru: index arrays do not fit")
+        code = DTYPE_CODE[proj.dtype]
+        if longest == 1 and self.lru_step:
+            # single tokens: convolution, gates, recurrence and the state's update in one launch
+            self._call("llm_lru_step", _ptr(proj), proj.shape[1], int(y_col), int(x_col), _ptr(bias_y), _ptr(bias_x), _ptr(taps_w),
+                       _ptr(conv_bias), taps, _ptr(ra), _ptr(ri), _ptr(ra_bias), _ptr(ri_bias), _ptr(lam), float(decay_scale), _ptr(state),
+                       _ptr(state_slots), _ptr(cu_seqlens), _ptr(out), code, requests, width, blocks, 1 if write else 0, self._stream())
+            return out
         u = self._scratch("lru.u", tokens * width, proj.device)
         a = self._scratch("lru.a", tokens * width, proj.device)
         b = self._scratch("lru.b", tokens * width, proj.device)
-        code = DTYPE_CODE[proj.dtype]
         self._call("llm_lru_conv", _ptr(proj), proj.shape[1], int(x_col), _ptr(bias_x), _ptr(taps_w), _ptr(conv_bias), taps, _ptr(state),
                    _ptr(state_slots), _ptr(token_request), _ptr(cu_seqlens), _ptr(u), code, tokens, width, self._stream())
         self._call("llm_lru_gates", _ptr(u), _ptr(ra), _ptr(ri), _ptr(ra_bias), _ptr(ri_bias), _ptr(lam), float(decay_scale), _ptr(a),

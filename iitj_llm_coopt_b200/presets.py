@@ -128,6 +128,35 @@ FOMERAX_3B = fomerax_shape(3072, 8192, 24, 8, 128, 128256, blocks=2, q_rank=1024
 FOMERAX_1B = fomerax_shape(2048, 8192, 32, 8, 64, 128256, blocks=2, q_rank=768, side_dim=128)
 FOMERAX_TOY = fomerax_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=128, kv_rank=128, rot_dim=32, q_rank=192, experts=4, side_dim=32)
 
+def mamusun_shape(width, inner, heads, kv_heads, head_dim, vocab, blocks, window=1024, experts=8, top=2, lru_blocks=16, taps=4,
+                  alpha=3.0) -> dict:
+    """A Mamusun config.json of `blocks` groups of four layers (sink attention with a dense feed-forward, window attention with
+    routed ones, window attention beside a gated recurrence with a dense one, window attention on the second layer's keys and
+    values with routed ones) at the layer sizes of a Llama of the same width: for runs with random weights beside the Rodapel and
+    the Llama of that size.  A routed layer holds `experts` experts of half the dense inner width; the recurrence is as wide as
+    the model."""
+    sink = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+            "rot": {"dims": head_dim, "base": 250000.0, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": window}}
+    left = dict(att, rot={"dims": head_dim // 4, "base": 10000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}})
+    par = {"left": left, "right": {"width": width, "blocks": lru_blocks, "conv": taps}}
+    dense = {"kind": "dense", "ff": inner}
+    routed = {"kind": "moe", "expert": {"ff": inner // 2, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+    layers = []
+    for b in range(blocks):
+        layers += [{"type": "attention_2", "mixer": copy.deepcopy(sink), "mlp": dict(dense)},
+                   {"type": "attention", "mixer": copy.deepcopy(att), "mlp": copy.deepcopy(routed)},
+                   {"type": "parallel", "mixer": copy.deepcopy(par), "mlp": dict(dense)},
+                   {"type": "attention", "mixer": dict(copy.deepcopy(att), kv_from=4 * b + 1), "mlp": copy.deepcopy(routed)}]
+    return {"architecture": "Mamusun", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "postln_alpha": alpha, "layers": layers}
+
+
+# Mamusun at the layer sizes of the Llama shapes above (8 layers each)
+MAMUSUN_8B = mamusun_shape(4096, 14336, 32, 8, 128, 128256, blocks=2)
+MAMUSUN_3B = mamusun_shape(3072, 8192, 24, 8, 128, 128256, blocks=2, lru_blocks=12)
+MAMUSUN_1B = mamusun_shape(2048, 8192, 32, 8, 64, 128256, blocks=2, lru_blocks=8)
+MAMUSUN_TOY = mamusun_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=128, experts=4, lru_blocks=4)
+
 # name -> (label used in reports, config.json dict)
 SHAPES = {
     "8b": ("llama-3.1-8b-shape-random", LLAMA_3_1_8B),
@@ -148,6 +177,10 @@ SHAPES = {
     "fomerax-3b": ("fomerax-3b-layers-random", FOMERAX_3B),
     "fomerax-1b": ("fomerax-1b-layers-random", FOMERAX_1B),
     "fomerax-toy": ("fomerax-toy-layers-random", FOMERAX_TOY),
+    "mamusun-8b": ("mamusun-8b-layers-random", MAMUSUN_8B),
+    "mamusun-3b": ("mamusun-3b-layers-random", MAMUSUN_3B),
+    "mamusun-1b": ("mamusun-1b-layers-random", MAMUSUN_1B),
+    "mamusun-toy": ("mamusun-toy-layers-random", MAMUSUN_TOY),
 }
 
 

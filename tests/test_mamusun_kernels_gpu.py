@@ -278,3 +278,9 @@ def test_gated_recurrence_in_portions_segments_and_reused_slots(K, dtype, width,
         close(again[r], want[r], dtype)
     if dtype == torch.float32:
         assert max((again[r] - got[r]).abs().max().item() for r in (0, 1)) < 1e-5
+    # two requests side by side, one token a step (the one-launch form), one of them ending early
+    state.zero_()
+    single = [[(1, 1, i, 1), (2, 3, i, 1)] if i < 9 else [(1, 1, i, 1)] for i in range(25)]
+    one = run(K, state, single)
+    close(one[2], want[2], dtype)
+    close(one[1], want[1][:25], dtype)
