@@ -163,9 +163,11 @@ class MamusunConfig:
             scaling = tuple(sorted({"type": "yarn", "factor": float(sc["factor"]), "original": float(sc["original"]),
                                     "fast": float(sc["fast"]), "slow": float(sc["slow"])}.items()))
         elif sc is not None:
-            scaling = tuple(sorted({"type": "llama3", "factor": float(sc["factor"]), "low_freq_factor": float(sc["low"]),
+            scaling = tuple(sorted({"type": "llama3", "float64": True, "factor": float(sc["factor"]), "low_freq_factor": float(sc["low"]),
                                     "high_freq_factor": float(sc["high"]),
                                     "original_max_position_embeddings": float(sc["original"])}.items()))
+        else:
+            scaling = (("float64", True), ("type", "none"))
         return PositionSpec(kind="rope", head_dim=int(m["dim"]), rotary_dim=int(rot["dims"]), theta=float(rot["base"]),
                             scaling=scaling, max_position=_MAX_POSITION, pairing=pairing)
 

@@ -75,10 +75,31 @@ __device__ __forceinline__ void load8(const float* p, int n, bool vec, float (&v
     }
 }
 
+// Eight neighbouring numbers as they are stored (16-byte reads), converted later: what a thread holds of the next k chunk while it
+// computes the current one.
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> {
+    uint4 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void get(float (&f)[8]) const {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 x = __bfloat1622float2(h[j]); f[2 * j] = x.x; f[2 * j + 1] = x.y; }
+    }
+};
+template <> struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *reinterpret_cast<const float4*>(p); b = *reinterpret_cast<const float4*>(p + 4); }
+    __device__ __forceinline__ void get(float (&f)[8]) const {
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+};
+
 // Both gate products as FMA tiles: a thread holds 8 tokens x 4 outputs of each matrix; operands pass through shared memory with k as
 // the slow index, so that a thread's tokens and outputs are neighbours (float4 reads); the sum along k runs in its natural order.
+// A thread whose rows and chunk lie wholly inside reads its share of the next chunk into registers before it computes the current one.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 lru_gates_kernel(const float* __restrict__ u, const T* __restrict__ ra, const T* __restrict__ ri, const float* __restrict__ ra_bias,
                  const float* __restrict__ ri_bias, const float* __restrict__ lam, float decay_scale, float* __restrict__ a_out,
                  float* __restrict__ b_out, int tokens, int width, int blocks) {
@@ -101,29 +122,37 @@ lru_gates_kernel(const float* __restrict__ u, const T* __restrict__ ra, const T*
     const T* wi = ri + (size_t)blk * bs * bs;
     const bool wvec = bs % 8 == 0 && !((uintptr_t)ra & 15) && !((uintptr_t)ri & 15);
     const bool uvec = width % 4 == 0 && bs % 4 == 0 && !((uintptr_t)u & 15);
+    const int ur = threadIdx.x / 4, ukq = (threadIdx.x % 4) * 4;       // this thread's share of u: four k of one token
+    const int wr = threadIdx.x / 2, wkg = (threadIdx.x % 2) * 8;       // and of both matrices: eight k of one output row
+    const float* up = u + (size_t)(t0 + ur) * width + blk * bs + ukq;
+    const T* wap = wa + (size_t)(n0 + wr) * bs + wkg;
+    const T* wip = wi + (size_t)(n0 + wr) * bs + wkg;
+    const bool inside = wvec && uvec && t0 + ur < tokens && n0 + wr < bs;
+    float4 next_u;
+    Raw8<T> next_a, next_i;
+    bool have = inside && GK <= bs;
+    if (have) { next_u = *reinterpret_cast<const float4*>(up); next_a.load(wap); next_i.load(wip); }
     for (int k0 = 0; k0 < bs; k0 += GK) {
-        {   // u: one run of four k per thread
-            const int r = threadIdx.x / 4, kq = (threadIdx.x % 4) * 4;
-            const int left = t0 + r < tokens ? bs - (k0 + kq) : 0;
-            const float* p = u + (size_t)(t0 + r) * width + blk * bs + k0 + kq;
-            float v[4];
-            if (uvec && left >= 4) { const float4 f = *reinterpret_cast<const float4*>(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
-            else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = j < left ? p[j] : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) us[kq + j][r] = v[j];
-        }
-        {   // both matrices: one run of eight k of one output row per thread
-            const int r = threadIdx.x / 2, kg = (threadIdx.x % 2) * 8;
-            const int left = n0 + r < bs ? bs - (k0 + kg) : 0;
+        if (have) {
             float va[8], vi[8];
-            load8(wa + (size_t)(n0 + r) * bs + k0 + kg, left, wvec, va);
-            load8(wi + (size_t)(n0 + r) * bs + k0 + kg, left, wvec, vi);
+            next_a.get(va);
+            next_i.get(vi);
+            us[ukq][ur] = next_u.x; us[ukq + 1][ur] = next_u.y; us[ukq + 2][ur] = next_u.z; us[ukq + 3][ur] = next_u.w;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { was[kg + j][r] = va[j]; wis[kg + j][r] = vi[j]; }
+            for (int j = 0; j < 8; ++j) { was[wkg + j][wr] = va[j]; wis[wkg + j][wr] = vi[j]; }
+        } else {
+            const int uleft = t0 + ur < tokens ? bs - (k0 + ukq) : 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) us[ukq + j][ur] = j < uleft ? up[k0 + j] : 0.f;
+            const int wleft = n0 + wr < bs ? bs - (k0 + wkg) : 0;
+            float va[8], vi[8];
+            load8(wap + k0, wleft, false, va);
+            load8(wip + k0, wleft, false, vi);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { was[wkg + j][wr] = va[j]; wis[wkg + j][wr] = vi[j]; }
         }
+        have = inside && k0 + 2 * GK <= bs;
+        if (have) { next_u = *reinterpret_cast<const float4*>(up + k0 + GK); next_a.load(wap + k0 + GK); next_i.load(wip + k0 + GK); }
         __syncthreads();
 #pragma unroll
         for (int k = 0; k < GK; ++k) {
@@ -160,19 +189,17 @@ lru_gates_kernel(const float* __restrict__ u, const T* __restrict__ ra, const T*
         }
 }
 
-// The new rows of z of a request's state, for channel c: the last taps - 1 of (old rows, this portion's rows).
+// The new rows of z of a request's state, for channel c: the last taps - 1 of (old rows, this portion's rows).  Row j is filled in
+// rising order from a row behind it (an old row further on, or one of the portion's), so nothing that is still needed is overwritten.
 template <typename T>
 __device__ __forceinline__ void lru_shift_state(float* st, const T* __restrict__ proj, int ld, int x_col, const float* __restrict__ bias_x,
                                                 int taps, int start, int end, int width, int c) {
-    const int keep = taps - 1, n = end - start;
-    float held[8];
+    const int keep = taps - 1;
     for (int j = 0; j < keep; ++j) {
-        const int src = end - keep + j;                 // token row; before `start`: the state's row keep + (src - start)
-        held[j] = src >= start ? to_f32(proj[(size_t)src * ld + x_col + c]) + (bias_x ? bias_x[c] : 0.f)
-                               : st[(size_t)(1 + keep + src - start) * width + c];
+        const int src = end - keep + j;                 // token row; before `start`: the state's row 1 + keep + (src - start) > 1 + j
+        st[(size_t)(1 + j) * width + c] = src >= start ? to_f32(proj[(size_t)src * ld + x_col + c]) + (bias_x ? bias_x[c] : 0.f)
+                                                       : st[(size_t)(1 + keep + src - start) * width + c];
     }
-    (void)n;
-    for (int j = 0; j < keep; ++j) st[(size_t)(1 + j) * width + c] = held[j];
 }
 
 template <typename T>
@@ -202,7 +229,7 @@ lru_scan_walk_kernel(const float* __restrict__ a, const float* __restrict__ b, c
 // (request, gate block): it holds the block's u in shared memory, a warp per output row walks k with its lanes (a fixed order), and
 // since no other block reads this block's channels of the state, it brings them up to date itself.
 template <typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 lru_step_kernel(const T* __restrict__ proj, int ld, int y_col, int x_col, const float* __restrict__ bias_y, const float* __restrict__ bias_x,
                 const float* __restrict__ taps_w, const float* __restrict__ conv_bias, int taps, const T* __restrict__ ra,
                 const T* __restrict__ ri, const float* __restrict__ ra_bias, const float* __restrict__ ri_bias, const float* __restrict__ lam,
@@ -229,6 +256,13 @@ lru_step_kernel(const T* __restrict__ proj, int ld, int y_col, int x_col, const 
     const bool vec = bs % 8 == 0 && !((uintptr_t)ra & 15) && !((uintptr_t)ri & 15);
     const int nwarp = blockDim.x >> 5;
     for (int n0 = warp * 4; n0 < bs; n0 += nwarp * 4) {      // four rows a warp at a time, a lane takes runs of eight k
+        // what lane r needs for row n0 + r after the sums is asked for first, so that it arrives while the weights do
+        const int n = n0 + lane;
+        const bool mine = lane < 4 && n < bs;
+        const int ch = blk * bs + (mine ? n : 0);
+        const float e_rab = mine ? ra_bias[ch] : 0.f, e_rib = mine ? ri_bias[ch] : 0.f, e_lam = mine ? lam[ch] : 0.f;
+        const float e_s = mine ? st[ch] : 0.f;
+        const float e_y = mine ? to_f32(proj[(size_t)t * ld + y_col + ch]) + (bias_y ? bias_y[ch] : 0.f) : 0.f;
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, si[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = lane * 8; k < bs; k += 256) {
             float uv[8];
@@ -250,15 +284,12 @@ lru_step_kernel(const T* __restrict__ proj, int ld, int y_col, int x_col, const 
             const float ta = warp_sum(sa[r]), ti = warp_sum(si[r]);
             if (lane == r) { ma = ta; mi = ti; }
         }
-        const int n = n0 + lane;
-        if (lane < 4 && n < bs) {
-            const int ch = blk * bs + n;
-            const float g = 1.0f / (1.0f + expf(-(ma + ra_bias[ch])));
-            const float gi = 1.0f / (1.0f + expf(-(mi + ri_bias[ch])));
-            const float l = lam[ch];
-            const float a = expf(-decay_scale * g * (l > 20.f ? l : log1pf(expf(l))));
-            const float S = fmaf(a, st[ch], sqrtf(fmaxf(1.0f - a * a, 0.f)) * gi * step_u[n]);
-            out[(size_t)t * width + ch] = from_f32<T>(S * gelu_tanh_lru(to_f32(proj[(size_t)t * ld + y_col + ch]) + (bias_y ? bias_y[ch] : 0.f)));
+        if (mine) {
+            const float g = 1.0f / (1.0f + expf(-(ma + e_rab)));
+            const float gi = 1.0f / (1.0f + expf(-(mi + e_rib)));
+            const float a = expf(-decay_scale * g * (e_lam > 20.f ? e_lam : log1pf(expf(e_lam))));
+            const float S = fmaf(a, e_s, sqrtf(fmaxf(1.0f - a * a, 0.f)) * gi * step_u[n]);
+            out[(size_t)t * width + ch] = from_f32<T>(S * gelu_tanh_lru(e_y));
             if (write) st[ch] = S;
         }
     }
@@ -345,7 +376,7 @@ LLM_API int llm_lru_conv(const void* proj, int ld, int x_col, const float* bias_
                          const float* state, const int* state_slots, const int* token_request, const int* cu_seqlens, float* u,
                          int dtype, int tokens, int width, cudaStream_t stream) {
     if (tokens == 0) return 0;
-    if (taps < 1 || taps > 9) LLM_FAIL(-1, "lru_conv: %d taps (1 to 9)", taps);
+    if (taps < 1) LLM_FAIL(-1, "lru_conv: %d taps", taps);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
         llm_launch(lru_conv_kernel<T>, (unsigned)tokens, 256, 0, stream, (const T*)proj, ld, x_col, bias_x, taps_w, conv_bias, taps, state,
@@ -379,7 +410,7 @@ LLM_API int llm_lru_scan(const float* a, const float* b, const void* proj, int l
                          const float* bias_x, int taps, float* state, const int* state_slots, const int* cu_seqlens, void* out,
                          int dtype, int requests, int width, int longest, int write, float* scratch, cudaStream_t stream) {
     if (requests == 0 || longest == 0) return 0;
-    if (taps < 1 || taps > 9) LLM_FAIL(-1, "lru_scan: %d taps (1 to 9)", taps);
+    if (taps < 1) LLM_FAIL(-1, "lru_scan: %d taps", taps);
     const unsigned cb = (unsigned)((width + 127) / 128);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
@@ -413,7 +444,7 @@ LLM_API int llm_lru_step(const void* proj, int ld, int y_col, int x_col, const f
                          const float* lam, float decay_scale, float* state, const int* state_slots, const int* cu_seqlens, void* out,
                          int dtype, int requests, int width, int blocks, int write, cudaStream_t stream) {
     if (requests == 0) return 0;
-    if (taps < 1 || taps > 9) LLM_FAIL(-1, "lru_step: %d taps (1 to 9)", taps);
+    if (taps < 1) LLM_FAIL(-1, "lru_step: %d taps", taps);
     if (blocks < 1 || width % blocks) LLM_FAIL(-1, "lru_step: width %d is not a multiple of %d blocks", width, blocks);
     if (requests > 65535) LLM_FAIL(-1, "lru_step: too many requests");
     const size_t smem = (size_t)(width / blocks) * sizeof(float);
@@ -421,7 +452,7 @@ LLM_API int llm_lru_step(const void* proj, int ld, int y_col, int x_col, const f
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
         if (smem > 48 * 1024) cudaFuncSetAttribute(lru_step_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llm_launch(lru_step_kernel<T>, dim3((unsigned)blocks, (unsigned)requests), 512, smem, stream, (const T*)proj, ld, y_col, x_col, bias_y,
+        llm_launch(lru_step_kernel<T>, dim3((unsigned)blocks, (unsigned)requests), width / blocks >= 128 ? 1024 : 256, smem, stream, (const T*)proj, ld, y_col, x_col, bias_y,
                    bias_x, taps_w, conv_bias, taps, (const T*)ra, (const T*)ri, ra_bias, ri_bias, lam, decay_scale, state, state_slots,
                    cu_seqlens, (T*)out, width, blocks, write);
         LLM_CHECK_LAUNCH("lru_step");

@@ -24,10 +24,12 @@ from .base import Part
 
 
 def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling: dict | None) -> torch.Tensor:
-    """float32 [rotary_dim/2]; llama3 scaling as engine/model.py:71-82."""
-    inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.int64).float() / rotary_dim))
+    """float32 [rotary_dim/2]; llama3 scaling as engine/model.py:71-82.  A scaling dict with a true "float64" entry has the
+    frequencies (and the law, if it names one) worked out in double precision and rounded to float32 once, at the end."""
+    dt = torch.float64 if scaling and scaling.get("float64") else torch.float32
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.int64).to(dt) / rotary_dim))
     if not scaling or scaling.get("rope_type", scaling.get("type")) != "llama3":
-        return inv_freq
+        return inv_freq.float()
     factor, lo, hi = scaling["factor"], scaling["low_freq_factor"], scaling["high_freq_factor"]
     old = scaling["original_max_position_embeddings"]
     low_wavelen, high_wavelen = old / lo, old / hi

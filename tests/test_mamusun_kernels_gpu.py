@@ -227,7 +227,7 @@ def test_route_by_softmax_over_the_chosen(K, outputs, top):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width,blocks,taps", [(16, 2, 4), (48, 3, 2), (200, 1, 5), (256, 4, 3), (96, 96, 1)])
+@pytest.mark.parametrize("width,blocks,taps", [(16, 2, 4), (48, 3, 2), (200, 1, 5), (256, 4, 3), (96, 96, 1), (64, 2, 12)])
 def test_gated_recurrence_in_portions_segments_and_reused_slots(K, dtype, width, blocks, taps):
     """Three requests over four state slots: whole prompts of 150 tokens and more in one step (segments), the same in portions down to
     one token (the walk), two requests side by side, against the plain restatement run over each request whole; a slot that is
