@@ -129,16 +129,16 @@ FOMERAX_1B = fomerax_shape(2048, 8192, 32, 8, 64, 128256, blocks=2, q_rank=768, 
 FOMERAX_TOY = fomerax_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=128, kv_rank=128, rot_dim=32, q_rank=192, experts=4, side_dim=32)
 
 def mamusun_shape(width, inner, heads, kv_heads, head_dim, vocab, blocks, window=1024, experts=8, top=2, lru_blocks=16, taps=4,
-                  alpha=3.0) -> dict:
+                  alpha=2.0) -> dict:
     """A Mamusun config.json of `blocks` groups of four layers (sink attention with a dense feed-forward, window attention with
     routed ones, window attention beside a gated recurrence with a dense one, window attention on the second layer's keys and
     values with routed ones) at the layer sizes of a Llama of the same width: for runs with random weights beside the Rodapel and
     the Llama of that size.  A routed layer holds `experts` experts of half the dense inner width; the recurrence is as wide as
     the model."""
     sink = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
-            "rot": {"dims": head_dim, "base": 250000.0, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"dims": head_dim, "base": 500000.0, "scaling": {"factor": 16.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": window}}
-    left = dict(att, rot={"dims": head_dim // 4, "base": 10000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}})
+    left = dict(att, rot={"dims": head_dim // 2, "base": 50000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 2.0, "original": 8192}})
     par = {"left": left, "right": {"width": width, "blocks": lru_blocks, "conv": taps}}
     dense = {"kind": "dense", "ff": inner}
     routed = {"kind": "moe", "expert": {"ff": inner // 2, "limit": 7.0}, "router": {"experts": experts, "top": top}}

@@ -54,15 +54,15 @@ def test_layers_become_cache_entries_and_calls():
 
 
 def test_rotation_laws_agree_with_the_plain_ones():
-    for dims, base, sc in ((32, 10000.0, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}), (8, 50.0, {"factor": 8.0, "low": 1.0, "high": 2.0, "original": 16})):
+    for dims, base, sc in ((48, 20000.0, {"factor": 8.0, "low": 1.0, "high": 2.0, "original": 256}), (8, 50.0, {"factor": 8.0, "low": 1.0, "high": 2.0, "original": 16})):
         want, _ = plain.stretched_frequencies(dims, base, sc)
         got = rope_inverse_frequencies(dims, base, {"type": "llama3", "factor": sc["factor"], "low_freq_factor": sc["low"],
                                                     "high_freq_factor": sc["high"], "original_max_position_embeddings": sc["original"]})
         assert torch.allclose(got.double(), want, rtol=1e-6)
         assert not torch.allclose(want, plain.plain_frequencies(dims, base))
-    sc = {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}
-    want, amp = plain.ramped_frequencies(96, 250000.0, sc)
-    assert torch.allclose(yarn_frequencies(96, 250000.0, sc).double(), want, rtol=1e-6) and abs(amp - (0.1 * math.log(8.0) + 1.0)) < 1e-12
+    sc = {"factor": 16.0, "original": 1024, "fast": 16.0, "slow": 2.0}
+    want, amp = plain.ramped_frequencies(64, 500000.0, sc)
+    assert torch.allclose(yarn_frequencies(64, 500000.0, sc).double(), want, rtol=1e-6) and abs(amp - (0.1 * math.log(16.0) + 1.0)) < 1e-12
 
 
 def broken(change):

@@ -46,14 +46,14 @@ def draw(seed):
             kind = "attention"
         elif pick < 0.7:
             kv, dim = rng.choice([1, 2, 3, 8]), rng.choice([8, 16, 32, 64, 96, 128])
-            scaling = rng.choice([None, (rng.choice([2.0, 8.0, 32.0]), rng.choice([16, 64, 2048]), rng.choice([32.0, 8.0]), rng.choice([1.0, 2.0]))])
+            scaling = rng.choice([None, (rng.choice([2.0, 8.0, 32.0]), rng.choice([16, 64, 1024]), rng.choice([32.0, 8.0]), rng.choice([1.0, 2.0]))])
             m = sink_attention(kv * rng.choice([1, 2, 4]), kv, dim, dim ** -0.5 * rng.choice([1.0, 2.0]), rng.choice([2, 4, 8, dim]),
-                               base=rng.choice([100.0, 1e4, 2.5e5]), scaling=scaling)
+                               base=rng.choice([100.0, 1e4, 5e5]), scaling=scaling)
             kind = "attention_2"
         else:
             kv, dim = rng.choice([1, 2, 3]), rng.choice([8, 16, 32, 64, 128])
             blocks = rng.choice([1, 2, 4, 8])
-            scaling = rng.choice([None, (rng.choice([4.0, 8.0]), 1.0, rng.choice([2.0, 4.0]), rng.choice([16, 512]))])
+            scaling = rng.choice([None, (rng.choice([4.0, 8.0]), 1.0, rng.choice([2.0, 4.0]), rng.choice([16, 256]))])
             m = parallel(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([8, 16, 32, 64, 128]), dim ** -0.5 * rng.choice([1.0, 2.0]),
                          rng.choice(WINDOWS), rng.choice([2, 4, 8, dim]), blocks * rng.choice([3, 8, 16, 40, 64]), blocks, rng.choice([2, 3, 4, 5]),
                          base=rng.choice([100.0, 1e4]), scaling=scaling)
